@@ -83,6 +83,8 @@ class ModelSpec:
     head_name: Optional[str]  # None: the embedding matrix is the output matrix
     logit_scale: float = 1.0      # logits are multiplied by this
     embedding_scale: float = 1.0  # embedding rows are multiplied by this on their way into the residual stream
+    embedding_norm: Optional[PartSpec] = None   # a norm the embedding rows pass before the first layer
+    embedding_norm_name: Optional[str] = None   # its tensor-name prefix
 
     def validate(self) -> None:
         from ..errors import InvalidArgumentError

@@ -1,0 +1,244 @@
+// Linear attention with one constant decay per head.
+//
+// Per head a matrix S [d, dv] of 32-bit floats, zero at a request's start.  With q, k, v the silu
+// of their projections, for each token
+//
+//     S = lambda_h S + k v^T        o = S^T q
+//
+// and the concatenated heads' o is divided by its root mean square over the whole row, multiplied by a
+// weight per value and by sigmoid(gate) (lightning_finish_kernel).
+//
+// A block owns 32 value columns of a head's state for one job; a lane a column, the warps the rows
+// in turn (rows w, w + 4, ...), each thread's share of S in registers.  The operands of kStage
+// tokens (silu applied) are staged in shared memory; the four warps' partial outputs are added in
+// a fixed order.  Three kinds of job (own notation; a chunk is kChunk tokens of one entry, cut
+// where the entry's tokens start in the step):
+//   walk     a job is an entry: from the request's state (zero if fresh) over all its tokens,
+//            with outputs, leaving the new state.  Steps of few tokens and of single tokens.
+//   ends     a job is a chunk: from zero over the chunk, no outputs, leaving E_c = sum_s
+//            lambda^(len - 1 - s) k_s v_s^T in the chunk's scratch row.
+//   outputs  a job is a chunk: from the state at the chunk's start (the scratch row), with outputs.
+// Between ends and outputs, lightning_carry_kernel walks each entry's chunks: start_c = S;
+// S = lambda^len_c S + E_c; the request's new state is the last S.  Another cut of a prompt only
+// re-associates 32-bit sums.
+#include "common.cuh"
+
+constexpr int kChunk = 64;
+constexpr int kStage = 16;
+constexpr int kColumns = 32;
+constexpr int kRowWarps = 4;
+
+enum LightningMode { MODE_WALK = 0, MODE_ENDS = 1, MODE_OUTPUTS = 2 };
+
+struct LightningParams {
+  const float* proj;        // [tokens, proj_width] 32-bit pre-activations of q, k, v and the gate
+  long long proj_width;
+  int q_off, k_off, v_off, g_off;
+  const float* decay;       // [heads]
+  float* state;             // [slots, heads * d * dv]
+  const int* entry_starts;  // [entries + 1]
+  const int* state_slots;   // [entries]
+  const int* fresh;         // [entries]
+  float* raw;               // [tokens, heads * dv] outputs before the norm
+  const float* norm_weight; // [heads * dv]
+  void* out;                // [tokens, heads * dv]
+  float* chunk_state;       // [jobs, heads * d * dv] (chunked form only)
+  int heads, d, dv, num_entries, num_tokens, num_jobs;
+  float eps;
+};
+
+__device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }
+
+// The chunk a job index names: (entry, first token, one past the last), or entry -1 past the last chunk.
+__device__ __forceinline__ void find_chunk(const int* __restrict__ entry_starts, int num_entries, int job, int* entry,
+                                           int* begin, int* end) {
+  int base = 0;
+  *entry = -1;
+  for (int e = 0; e < num_entries; ++e) {
+    const int start = entry_starts[e], stop = entry_starts[e + 1];
+    const int chunks = (stop - start + kChunk - 1) / kChunk;
+    if (job < base + chunks) {
+      *entry = e;
+      *begin = start + (job - base) * kChunk;
+      *end = min(*begin + kChunk, stop);
+      return;
+    }
+    base += chunks;
+  }
+}
+
+template <int RPT, int MODE>
+__global__ void __launch_bounds__(kRowWarps * 32)
+lightning_scan_kernel(LightningParams p) {
+  extern __shared__ float shared[];
+  float* q_s = shared;                       // [kStage][d]
+  float* k_s = q_s + kStage * p.d;           // [kStage][d]
+  float* v_s = k_s + kStage * p.d;           // [kStage][kColumns]
+  float* part = v_s + kStage * kColumns;     // [kStage][kRowWarps][kColumns]
+  __shared__ int job_info[3];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, job = blockIdx.z;
+  const int column = blockIdx.x * kColumns + lane;
+  const bool live = column < p.dv;
+  int entry, begin, end;
+  if (MODE == MODE_WALK) {
+    entry = job;
+    begin = p.entry_starts[entry];
+    end = p.entry_starts[entry + 1];
+  } else {
+    if (threadIdx.x == 0) find_chunk(p.entry_starts, p.num_entries, job, &job_info[0], &job_info[1], &job_info[2]);
+    __syncthreads();
+    entry = job_info[0], begin = job_info[1], end = job_info[2];
+    if (entry < 0) return;
+  }
+  if (end <= begin) return;
+  const float lambda = p.decay[h];
+  const size_t state_size = static_cast<size_t>(p.heads) * p.d * p.dv;
+  float* own = MODE == MODE_WALK ? p.state + static_cast<size_t>(p.state_slots[entry]) * state_size
+                                 : p.chunk_state + static_cast<size_t>(job) * state_size;
+  own += static_cast<size_t>(h) * p.d * p.dv;
+  float s[RPT];
+  const bool load = MODE == MODE_OUTPUTS || (MODE == MODE_WALK && !p.fresh[entry]);
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int row = warp + kRowWarps * i;
+    s[i] = (load && live && row < p.d) ? own[static_cast<size_t>(row) * p.dv + column] : 0.0f;
+  }
+  for (int base = begin; base < end; base += kStage) {
+    const int count = min(kStage, end - base);
+    __syncthreads();
+    for (int i = threadIdx.x; i < count * p.d; i += blockDim.x) {
+      const int tt = i / p.d, e = i % p.d;
+      const float* row = p.proj + static_cast<size_t>(base + tt) * p.proj_width;
+      if (MODE != MODE_ENDS) q_s[tt * p.d + e] = silu(row[p.q_off + h * p.d + e]);
+      k_s[tt * p.d + e] = silu(row[p.k_off + h * p.d + e]);
+    }
+    for (int i = threadIdx.x; i < count * kColumns; i += blockDim.x) {
+      const int tt = i / kColumns, c = blockIdx.x * kColumns + i % kColumns;
+      v_s[i] = c < p.dv ? silu(p.proj[static_cast<size_t>(base + tt) * p.proj_width + p.v_off + h * p.dv + c]) : 0.0f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < count; ++tt) {
+      const float v = v_s[tt * kColumns + lane];
+      float o = 0.0f;
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) {
+        const int row = warp + kRowWarps * i;
+        if (row < p.d) {
+          s[i] = fmaf(lambda, s[i], k_s[tt * p.d + row] * v);
+          if (MODE != MODE_ENDS) o = fmaf(s[i], q_s[tt * p.d + row], o);
+        }
+      }
+      if (MODE != MODE_ENDS) part[(tt * kRowWarps + warp) * kColumns + lane] = o;
+    }
+    if (MODE != MODE_ENDS) {
+      __syncthreads();
+      for (int i = threadIdx.x; i < count * kColumns; i += blockDim.x) {
+        const int tt = i / kColumns, l = i % kColumns, c = blockIdx.x * kColumns + l;
+        if (c < p.dv) {
+          const float* o = part + tt * kRowWarps * kColumns + l;
+          p.raw[static_cast<size_t>(base + tt) * (p.heads * p.dv) + h * p.dv + c] =
+              ((o[0] + o[kColumns]) + o[2 * kColumns]) + o[3 * kColumns];
+        }
+      }
+    }
+  }
+  if (MODE != MODE_OUTPUTS && live) {
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int row = warp + kRowWarps * i;
+      if (row < p.d) own[static_cast<size_t>(row) * p.dv + column] = s[i];
+    }
+  }
+}
+
+// One thread per element of a head's state and entry: the entry's chunks in a row.
+__global__ void __launch_bounds__(256)
+lightning_carry_kernel(LightningParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int entry = blockIdx.y;
+  const size_t state_size = static_cast<size_t>(p.heads) * p.d * p.dv;
+  const size_t element = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (element >= state_size) return;
+  const int start = p.entry_starts[entry], stop = p.entry_starts[entry + 1];
+  if (stop <= start) return;
+  int job = 0;
+  for (int e = 0; e < entry; ++e) job += (p.entry_starts[e + 1] - p.entry_starts[e] + kChunk - 1) / kChunk;
+  const float lambda = p.decay[element / (static_cast<size_t>(p.d) * p.dv)];
+  float* own = p.state + static_cast<size_t>(p.state_slots[entry]) * state_size + element;
+  float s = p.fresh[entry] ? 0.0f : *own;
+  float whole = 1.0f;   // lambda^kChunk by repeated multiplication, the same way the scan applies it
+  for (int i = 0; i < kChunk; ++i) whole *= lambda;
+  for (int begin = start; begin < stop; begin += kChunk, ++job) {
+    const int length = min(kChunk, stop - begin);
+    float* slot = p.chunk_state + static_cast<size_t>(job) * state_size + element;
+    const float ending = *slot;
+    *slot = s;
+    float power = whole;
+    if (length < kChunk) {
+      power = 1.0f;
+      for (int i = 0; i < length; ++i) power *= lambda;
+    }
+    s = fmaf(power, s, ending);
+  }
+  *own = s;
+}
+
+// The norm over the concatenated heads, the norm's weight and the output gate; a block per token.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+lightning_finish_kernel(LightningParams p) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int width = p.heads * p.dv;
+  const float* raw = p.raw + static_cast<size_t>(t) * width;
+  const float* gate = p.proj + static_cast<size_t>(t) * p.proj_width + p.g_off;
+  float sum = 0.0f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) sum += raw[i] * raw[i];
+  const float inverse = 1.0f / sqrtf(block_sum(sum, scratch) / static_cast<float>(width) + p.eps);
+  TO* out = static_cast<TO*>(p.out) + static_cast<size_t>(t) * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    out[i] = from_float<TO>(raw[i] * inverse * p.norm_weight[i] * (1.0f / (1.0f + expf(-gate[i]))));
+}
+
+template <int RPT>
+static int launch_scans(const LightningParams& p, bool chunked, cudaStream_t s) {
+  const size_t shared = (static_cast<size_t>(2 * kStage) * p.d + kStage * kColumns + kStage * kRowWarps * kColumns) * sizeof(float);
+  const int tiles = (p.dv + kColumns - 1) / kColumns;
+  if (!chunked)
+    return vipera_launch(lightning_scan_kernel<RPT, MODE_WALK>, dim3(tiles, p.heads, p.num_entries), kRowWarps * 32, shared, s, p);
+  int status = vipera_launch(lightning_scan_kernel<RPT, MODE_ENDS>, dim3(tiles, p.heads, p.num_jobs), kRowWarps * 32, shared, s, p);
+  if (status) return status;
+  const size_t state_size = static_cast<size_t>(p.heads) * p.d * p.dv;
+  status = vipera_launch(lightning_carry_kernel, dim3(static_cast<unsigned>((state_size + 255) / 256), p.num_entries), 256, 0, s, p);
+  if (status) return status;
+  return vipera_launch(lightning_scan_kernel<RPT, MODE_OUTPUTS>, dim3(tiles, p.heads, p.num_jobs), kRowWarps * 32, shared, s, p);
+}
+
+// num_jobs > 0 (with chunk_state): the chunked form, num_jobs at least the step's count of chunks.
+VIPERA_API int vipera_lightning(const LightningParams* params, int out_dtype, void* stream) {
+  const LightningParams& p = *params;
+  if (p.num_tokens <= 0 || p.num_entries <= 0) return VIPERA_OK;
+  if (p.heads <= 0 || p.d <= 0 || p.d > 256 || p.dv <= 0 || p.heads > 65535 || p.num_entries > 65535) return VIPERA_BAD_SHAPE;
+  const bool chunked = p.num_jobs > 0;
+  if (chunked && (p.chunk_state == nullptr || p.num_jobs > 65535)) return VIPERA_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int status;
+  if (p.d <= 32) status = launch_scans<8>(p, chunked, s);
+  else if (p.d <= 64) status = launch_scans<16>(p, chunked, s);
+  else if (p.d <= 128) status = launch_scans<32>(p, chunked, s);
+  else status = launch_scans<64>(p, chunked, s);
+  if (status) return status;
+  if (out_dtype == VIPERA_F32) return vipera_launch(lightning_finish_kernel<float>, p.num_tokens, 256, 0, s, p);
+  if (out_dtype == VIPERA_BF16) return vipera_launch(lightning_finish_kernel<__nv_bfloat16>, p.num_tokens, 256, 0, s, p);
+  return VIPERA_BAD_DTYPE;
+}
+
+VIPERA_API int vipera_lightning_params_size() { return static_cast<int>(sizeof(LightningParams)); }
+VIPERA_API int vipera_lightning_chunk() { return kChunk; }
+VIPERA_API const char* vipera_lightning_status_text(int status) { return vipera_status_text(status); }

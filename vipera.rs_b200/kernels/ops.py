@@ -93,11 +93,12 @@ class KernelProfile:
         "gemm_tc": "proj", "gemm_tc_rope": "proj", "gemv_small": "proj", "gemm_simt": "proj",
         "attention": "attention", "attention_prefill": "attention", "attention_prefill_tc": "attention",
         "attention_decode": "attention", "mlstm": "recurrence", "mamba_scan": "recurrence", "gla": "recurrence",
+        "lightning": "recurrence", "moe": "experts",
         "layernorm": "norm", "causal_conv": "conv",
         "argmax": "sample", "sample": "sample", "apply_penalties": "sample", "feed_tokens": "sample",
         "logprobs": "sample",
     }
-    ORDER = ("proj", "attention", "recurrence", "norm", "conv", "rope_kv", "embed", "sample", "other")
+    ORDER = ("proj", "experts", "attention", "recurrence", "norm", "conv", "rope_kv", "embed", "sample", "other")
 
     def __init__(self):
         self._events = []
@@ -1379,3 +1380,232 @@ def gla(proj: torch.Tensor, z: torch.Tensor, *, offsets, heads: int, dim: int, v
         p.chunk_state = _gpu(chunk_state, "chunk states", torch.float32)
         p.chunk_decay = _gpu(chunk_decay, "chunk decays", torch.float32)
     _check(fn(ctypes.byref(p), dtype_code(out.dtype), _stream()), "gla", kernels=5 if chunk_scratch is not None else 3)
+
+
+# ----------------------------------------------------------------------------------------
+# norms over groups of a row, and a sublayer's gated, normed and scaled way into the stream
+# ----------------------------------------------------------------------------------------
+def group_rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, groups: int,
+                  rows: Optional[torch.Tensor] = None) -> None:
+    """out[r, g, :] = x[rows[r], g, :] / sqrt(mean(x[rows[r], g, :]^2) + eps) * weight[g, :]: the row
+    is cut into ``groups`` equal consecutive parts, each divided by its own root mean square.  The
+    float32 ``out`` may be ``x`` itself (without ``rows``)."""
+    fn = _function("groupnorm", "vipera_group_rmsnorm",
+                   [_c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void])
+    hidden = x.shape[1]
+    count = out.shape[0]
+    if out.shape[1] != hidden or weight.numel() != hidden or hidden % int(groups):
+        raise InvalidArgumentError("group_rmsnorm: widths of x, weight and out do not agree, or the groups do not divide them")
+    if rows is None and x.shape[0] != count:
+        raise InvalidArgumentError("group_rmsnorm: x and out have different row counts")
+    if rows is not None and (rows.numel() != count or out.data_ptr() == x.data_ptr()):
+        raise InvalidArgumentError("group_rmsnorm: one row index per output row, and no norm in place with row indices")
+    _check(fn(_gpu(x, "x", torch.float32), _gpu(weight, "weight", torch.float32), _opt(rows, "rows", torch.int32),
+              _gpu(out, "out"), dtype_code(out.dtype), count, hidden, int(groups), float(eps), _stream()), "rmsnorm")
+
+
+def gated_norm_add(branch: torch.Tensor, parts: int, gate: Optional[torch.Tensor], coefficient: torch.Tensor,
+                   residual: torch.Tensor, eps: float, groups: int) -> None:
+    """``y = (sum_p branch[r, p, :]) * sigmoid(gate[r, :])`` (no gate: the sum itself), then
+    ``residual[r, g, :] += coefficient[g, :] * y[g, :] / sqrt(mean(y[g, :]^2) + eps)`` over ``groups``
+    equal parts of the row.  ``branch`` is float32 [rows, parts * hidden] (its first part is used
+    as scratch), ``gate`` float32 [rows, hidden] holds pre-activations."""
+    fn = _function("groupnorm", "vipera_gated_norm_add",
+                   [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_float, _c_void])
+    count, hidden = residual.shape
+    if branch.numel() != count * int(parts) * hidden or coefficient.numel() != hidden or hidden % int(groups):
+        raise InvalidArgumentError("gated_norm_add: shapes of the branch, the coefficients and the stream do not agree")
+    if gate is not None and tuple(gate.shape) != (count, hidden):
+        raise InvalidArgumentError("gated_norm_add: the gate must be [rows, hidden]")
+    _check(fn(_gpu(branch, "branch", torch.float32), int(parts), _opt(gate, "gate", torch.float32),
+              _gpu(coefficient, "coefficient", torch.float32), _gpu(residual, "residual", torch.float32), count, hidden,
+              int(groups), float(eps), _stream()), "rmsnorm")
+
+
+# ----------------------------------------------------------------------------------------
+# attention over a cached low-rank latent
+# ----------------------------------------------------------------------------------------
+class _LatentParams(ctypes.Structure):
+    _fields_ = [
+        ("proj", _c_void), ("proj_width", ctypes.c_longlong), ("q_off", _c_int), ("g_off", _c_int), ("kv_off", _c_int),
+        ("up_k", _c_void), ("up_v", _c_void), ("norm_weight", _c_void), ("positions", _c_void), ("token_entry", _c_void),
+        ("block_table", _c_void), ("cos_table", _c_void), ("sin_table", _c_void), ("k_pool", _c_void), ("v_pool", _c_void),
+        ("qa", _c_void), ("latent_out", _c_void), ("out", _c_void),
+        ("num_tokens", _c_int), ("heads", _c_int), ("d", _c_int), ("rot", _c_int), ("dv", _c_int), ("rank", _c_int),
+        ("table_width", _c_int), ("page_size", _c_int), ("scale", _c_float), ("eps", _c_float),
+    ]
+
+
+def latent_attention(proj: torch.Tensor, *, q_off: int, g_off: int, kv_off: int, up_k: torch.Tensor, up_v: torch.Tensor,
+                     norm_weight: Optional[torch.Tensor], eps: float, positions: torch.Tensor, token_entry: torch.Tensor,
+                     block_table: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, k_pool: torch.Tensor,
+                     v_pool: torch.Tensor, qa: torch.Tensor, latent_out: torch.Tensor, out: torch.Tensor, heads: int,
+                     head_dim: int, rot_dim: int, value_dim: int, scale: float) -> None:
+    """Causal softmax attention whose keys and values are products of a cached latent.  ``proj``
+    float32 [tokens, width] holds q (head by head [head_dim | rot_dim]) at column ``q_off``, the
+    output gate's pre-activation at ``g_off`` (negative: no gate) and the down projection
+    [rank | rot_dim] at ``kv_off`` (negative: the step's tokens are in the cache already, written
+    by another layer).  ``k_pool`` [pages, page_size, 1, rank] receives the normed latents,
+    ``v_pool`` [pages, page_size, 1, rot_dim] the rotated key part the heads share.  ``up_k``
+    [heads * head_dim, rank] and ``up_v`` [heads, rank, value_dim] (each head's value matrix
+    transposed) are in the pools' type, as is ``out`` [tokens, heads * value_dim]; ``qa`` float32
+    [tokens, heads, rank + rot_dim] and ``latent_out`` float32 [tokens, heads, rank] are scratch."""
+    fn = _function("latent", "vipera_latent_attention", [ctypes.POINTER(_LatentParams), _c_int, _c_void])
+    _check_struct("latent", "vipera_latent_params_size", _LatentParams)
+    tokens = proj.shape[0]
+    rank = k_pool.shape[3]
+    page_size = k_pool.shape[1]
+    if tuple(k_pool.shape[1:]) != (page_size, 1, rank) or tuple(v_pool.shape[1:]) != (page_size, 1, rot_dim) or \
+            k_pool.dtype != v_pool.dtype:
+        raise InvalidArgumentError("latent_attention: the pools must be [pages, page_size, 1, rank] and [pages, page_size, 1, rot_dim]")
+    if tuple(up_k.shape) != (heads * head_dim, rank) or tuple(up_v.shape) != (heads, rank, value_dim) or \
+            up_k.dtype != k_pool.dtype or up_v.dtype != k_pool.dtype or out.dtype != k_pool.dtype:
+        raise InvalidArgumentError("latent_attention: the up matrices and the output must match the pools' type and sizes")
+    if tuple(out.shape) != (tokens, heads * value_dim) or qa.numel() < tokens * heads * (rank + rot_dim) or \
+            latent_out.numel() < tokens * heads * rank:
+        raise InvalidArgumentError("latent_attention: the output or a scratch buffer is too small")
+    if tuple(cos.shape[1:]) != (rot_dim // 2,) or cos.shape != sin.shape:
+        raise InvalidArgumentError("latent_attention: cos/sin tables of width rot_dim/2 are needed")
+    if kv_off >= 0 and (norm_weight is None or norm_weight.numel() != rank):
+        raise InvalidArgumentError("latent_attention: a layer that writes the cache needs the latent's norm weight")
+    p = _LatentParams()
+    p.proj, p.proj_width = _gpu(proj, "proj", torch.float32), proj.shape[1]
+    p.q_off, p.g_off, p.kv_off = int(q_off), int(g_off), int(kv_off)
+    p.up_k, p.up_v = _gpu(up_k, "up_k"), _gpu(up_v, "up_v")
+    p.norm_weight = _opt(norm_weight, "norm_weight", torch.float32)
+    p.positions = _gpu(positions, "positions", torch.int32)
+    p.token_entry = _gpu(token_entry, "token_entry", torch.int32)
+    p.block_table = _gpu(block_table, "block_table", torch.int32)
+    p.cos_table, p.sin_table = _gpu(cos, "cos", torch.float32), _gpu(sin, "sin", torch.float32)
+    p.k_pool, p.v_pool = _gpu(k_pool, "k_pool"), _gpu(v_pool, "v_pool")
+    p.qa, p.latent_out = _gpu(qa, "qa", torch.float32), _gpu(latent_out, "latent_out", torch.float32)
+    p.out = _gpu(out, "out")
+    p.num_tokens, p.heads, p.d, p.rot, p.dv, p.rank = int(tokens), int(heads), int(head_dim), int(rot_dim), int(value_dim), int(rank)
+    p.table_width, p.page_size = int(block_table.shape[1]), int(page_size)
+    p.scale, p.eps = float(scale), float(eps)
+    _check(fn(ctypes.byref(p), dtype_code(k_pool.dtype), _stream()), "attention", kernels=4 if kv_off >= 0 else 3)
+
+
+# ----------------------------------------------------------------------------------------
+# linear attention with one constant decay per head
+# ----------------------------------------------------------------------------------------
+class _LightningParams(ctypes.Structure):
+    _fields_ = [
+        ("proj", _c_void), ("proj_width", ctypes.c_longlong),
+        ("q_off", _c_int), ("k_off", _c_int), ("v_off", _c_int), ("g_off", _c_int),
+        ("decay", _c_void), ("state", _c_void), ("entry_starts", _c_void), ("state_slots", _c_void), ("fresh", _c_void),
+        ("raw", _c_void), ("norm_weight", _c_void), ("out", _c_void), ("chunk_state", _c_void),
+        ("heads", _c_int), ("d", _c_int), ("dv", _c_int), ("num_entries", _c_int), ("num_tokens", _c_int),
+        ("num_jobs", _c_int), ("eps", _c_float),
+    ]
+
+
+def lightning(proj: torch.Tensor, *, offsets, heads: int, dim: int, vdim: int, decay: torch.Tensor,
+              norm_weight: torch.Tensor, norm_eps: float, state: torch.Tensor, entry_starts: torch.Tensor,
+              state_slots: torch.Tensor, fresh: torch.Tensor, num_entries: int, raw: torch.Tensor, out: torch.Tensor,
+              chunk_state: Optional[torch.Tensor] = None) -> None:
+    """Linear attention with a constant decay per head over a step: ``S = decay_h S + k v^T``,
+    ``o = S^T q`` with q, k, v the silu of their projections.  ``proj`` float32 [tokens, width]
+    holds the pre-activations of q, k, v and the output gate at ``offsets``; ``state`` float32
+    [slots, heads * dim * vdim]; ``raw`` float32 [tokens, heads * vdim] is scratch; ``out`` [tokens,
+    heads * vdim] receives the heads' outputs divided by their root mean square over the whole row,
+    times ``norm_weight`` and the sigmoid of the gate.  ``chunk_state`` (float32 [jobs, heads * dim *
+    vdim], jobs >= scan_jobs(tokens, entries)) lets the step's chunks of SCAN_CHUNK tokens run side
+    by side instead of each entry's tokens in a row."""
+    fn = _function("lightning", "vipera_lightning", [ctypes.POINTER(_LightningParams), _c_int, _c_void])
+    _check_struct("lightning", "vipera_lightning_params_size", _LightningParams)
+    tokens = proj.shape[0]
+    if tuple(out.shape) != (tokens, heads * vdim) or raw.numel() < tokens * heads * vdim or decay.numel() != heads or \
+            norm_weight.numel() != heads * vdim:
+        raise InvalidArgumentError("lightning: out must be [tokens, heads * value size], with one decay per head and one "
+                                   "norm weight per value of the row")
+    if state.dim() != 2 or state.shape[1] != heads * dim * vdim:
+        raise InvalidArgumentError("lightning: state rows must hold heads * d * value size floats")
+    p = _LightningParams()
+    p.proj, p.proj_width = _gpu(proj, "proj", torch.float32), proj.shape[1]
+    p.q_off, p.k_off, p.v_off, p.g_off = (int(o) for o in offsets)
+    p.decay, p.state = _gpu(decay, "decay", torch.float32), _gpu(state, "state", torch.float32)
+    p.entry_starts = _gpu(entry_starts, "entry_starts", torch.int32)
+    p.state_slots = _gpu(state_slots, "state_slots", torch.int32)
+    p.fresh = _gpu(fresh, "fresh", torch.int32)
+    p.raw, p.norm_weight = _gpu(raw, "raw", torch.float32), _gpu(norm_weight, "norm_weight", torch.float32)
+    p.out = _gpu(out, "out")
+    p.heads, p.d, p.dv, p.num_entries, p.num_tokens = int(heads), int(dim), int(vdim), int(num_entries), int(tokens)
+    p.eps = float(norm_eps)
+    if chunk_state is not None:
+        jobs = scan_jobs(tokens, num_entries)
+        if chunk_state.shape[0] < jobs or chunk_state.shape[1] != heads * dim * vdim:
+            raise InvalidArgumentError("lightning: the chunk scratch has the wrong shape")
+        p.num_jobs = jobs
+        p.chunk_state = _gpu(chunk_state, "chunk states", torch.float32)
+    _check(fn(ctypes.byref(p), dtype_code(out.dtype), _stream()), "lightning", kernels=4 if chunk_state is not None else 2)
+
+
+# ----------------------------------------------------------------------------------------
+# mixture of gated units
+# ----------------------------------------------------------------------------------------
+class _MoeParams(ctypes.Structure):
+    _fields_ = [
+        ("h", _c_void), ("router", _c_void), ("gate", _c_void), ("up", _c_void), ("down", _c_void),
+        ("chosen", _c_void), ("weight", _c_void), ("order", _c_void), ("rank", _c_void), ("tiles", _c_void),
+        ("act", _c_void), ("rows", _c_void),
+        ("num_tokens", _c_int), ("hidden", _c_int), ("ff", _c_int), ("experts", _c_int), ("top", _c_int),
+        ("groups", _c_int), ("keep", _c_int), ("group_top", _c_int), ("max_tiles", _c_int),
+        ("softmax_scores", _c_int), ("renormalize", _c_int), ("activation", _c_int),
+    ]
+
+
+MOE_TILE_ROWS = 32   # kTileRows in moe.cu
+
+
+def moe_max_tiles(tokens: int, top: int, experts: int) -> int:
+    """The most tiles of assignments a step of `tokens` tokens has."""
+    return tokens * top // MOE_TILE_ROWS + min(experts, tokens * top)
+
+
+def moe(h: torch.Tensor, *, router: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, top: int,
+        groups: int, keep: int, group_top: int, softmax_scores: bool, renormalize: bool, activation: int,
+        chosen: torch.Tensor, weight: torch.Tensor, scratch: torch.Tensor, act: torch.Tensor, rows: torch.Tensor) -> None:
+    """A mixture of gated units over a step.  ``h`` [tokens, hidden]; ``router`` float32 [experts,
+    hidden]; ``gate`` and ``up`` [experts, ff, hidden] and ``down`` [experts, hidden, ff] in h's
+    type.  ``chosen`` int32 and ``weight`` float32 [tokens, top] receive each token's experts and
+    their weights; ``rows`` float32 [tokens, top, hidden] receives each chosen expert's weighted
+    output (their sum over ``top`` is the mixture's output).  ``scratch`` int32 of at least 2 *
+    tokens * top + 1 + 3 * moe_max_tiles(...) words; ``act`` [tokens * top, ff] in h's type."""
+    fn = _function("moe", "vipera_moe", [ctypes.POINTER(_MoeParams), _c_int, _c_void])
+    _check_struct("moe", "vipera_moe_params_size", _MoeParams)
+    tokens, hidden = h.shape
+    experts, ff = gate.shape[0], gate.shape[1]
+    if tuple(router.shape) != (experts, hidden) or tuple(gate.shape) != (experts, ff, hidden) or up.shape != gate.shape or \
+            tuple(down.shape) != (experts, hidden, ff) or gate.dtype != h.dtype or up.dtype != h.dtype or down.dtype != h.dtype:
+        raise InvalidArgumentError("moe: the experts' matrices do not match h and each other")
+    assignments = tokens * int(top)
+    tiles = moe_max_tiles(tokens, int(top), experts)
+    if chosen.numel() < assignments or weight.numel() < assignments or scratch.numel() < 2 * assignments + 1 + 3 * tiles or \
+            act.numel() < assignments * ff or act.dtype != h.dtype or rows.numel() < assignments * hidden:
+        raise InvalidArgumentError("moe: a scratch buffer is too small")
+    p = _MoeParams()
+    p.h, p.router = _gpu(h, "h"), _gpu(router, "router", torch.float32)
+    p.gate, p.up, p.down = _gpu(gate, "gate"), _gpu(up, "up"), _gpu(down, "down")
+    p.chosen, p.weight = _gpu(chosen, "chosen", torch.int32), _gpu(weight, "weight", torch.float32)
+    base = _gpu(scratch, "scratch", torch.int32)
+    p.order, p.rank, p.tiles = base, base + 4 * assignments, base + 8 * assignments
+    p.act, p.rows = _gpu(act, "act"), _gpu(rows, "rows", torch.float32)
+    p.num_tokens, p.hidden, p.ff, p.experts, p.top = int(tokens), int(hidden), int(ff), int(experts), int(top)
+    p.groups, p.keep, p.group_top, p.max_tiles = int(groups), int(keep), int(group_top), int(tiles)
+    p.softmax_scores, p.renormalize, p.activation = int(bool(softmax_scores)), int(bool(renormalize)), int(activation)
+    _check(fn(ctypes.byref(p), dtype_code(h.dtype), _stream()), "moe", kernels=4)
+
+
+def add_rows(rows: torch.Tensor, parts: int, target: torch.Tensor) -> None:
+    """target[t, :] += sum_p rows[t, p, :] (float32), the places added in their order."""
+    fn = _function("moe", "vipera_moe_add_rows", [_c_void, _c_int, _c_void, _c_int, _c_int, _c_void])
+    count, hidden = target.shape
+    if rows.numel() != count * int(parts) * hidden:
+        raise InvalidArgumentError("add_rows: rows must hold parts rows of the target's width per token")
+    _check(fn(_gpu(rows, "rows", torch.float32), int(parts), _gpu(target, "target", torch.float32), count, hidden, _stream()),
+           "moe")
+
+
+LATENT_MAX_RANK, LATENT_MAX_ROT = 512, 128   # kMaxRank, kMaxRot in latent.cu
+MOE_MAX_EXPERTS = 1024                       # kMaxExperts in moe.cu

@@ -1,6 +1,6 @@
 """Parts a decoder is put together from.  Importing this package registers the built-in
-kinds: ``rmsnorm`` and ``layernorm``; ``rope_neox``, ``rope_interleaved`` and ``none``; ``gqa_attention``, ``mlstm``, ``mamba1``, ``gla`` and ``parallel``; ``swiglu`` (also ``gated_mlp``); ``prenorm``, ``prenorm_mixer`` and ``outnorm_conv``."""
-from . import attention, block, gla, mamba, mlp, mlstm, norm, parallel, rotary  # noqa: F401  (registration)
+kinds: ``rmsnorm`` and ``layernorm``; ``rope_neox``, ``rope_interleaved`` and ``none``; ``gqa_attention``, ``latent_attention``, ``mlstm``, ``mamba1``, ``gla``, ``lightning`` and ``parallel``; ``swiglu`` (also ``gated_mlp``) and ``moe_mlp``; ``prenorm``, ``prenorm_mixer``, ``outnorm_conv`` and ``sandwich``."""
+from . import attention, block, gla, latent, lightning, mamba, mlp, mlstm, moe, norm, parallel, rotary  # noqa: F401  (registration)
 from .base import (
     CacheBundle,
     FeedForward,

@@ -17,9 +17,13 @@ from typing import Dict
 import torch
 
 from ..config.registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Registry
+from ..errors import UnsupportedError
+from ..kernels import ops
+from ..weights import TensorSpec
 from .base import CacheBundle, FixedState, StateView
 from .conv import CausalConv
-from .linear import NormedInput
+from .linear import Linear, NormedInput
+from .norm import LayerNorm
 
 
 class Block:
@@ -201,6 +205,125 @@ class OutNormConvBlock(Block):
             self.ffn_norm.add_into(ctx, branch, residual)
 
 
+class SandwichBlock(Block):
+    """Norms before and after each sublayer, the sublayer's output gated by its own input and
+    scaled per channel, a constant multiplier on what joins the stream:
+
+        h = N(x);  y = sublayer(h) * sigmoid(R h + r);  x += m * s * Nb(y)
+
+    first for the mixer, then (where the layer has one) for the feed-forward.  ``params``:
+    ``hidden_size``, ``residual_mult`` (m), ``layer_scale`` (true: tensors ``<layer>.<mixer_scale>.weight``
+    and ``<layer>.<ffn_scale>.weight`` [hidden], the s above) and ``gated`` (true: matrices
+    ``<layer>.<mixer_gate>.weight`` [hidden, hidden] with ``.bias``, and the same for ``ffn_gate``).
+    The norms after the sublayers are of the RMS kind (a weight, an eps and a count of groups):
+    one kernel gates the sublayer's output, norms it, scales it and adds it into the stream.
+
+    A sublayer adds its output into the 32-bit stream it is handed; here that is a cleared buffer.
+    A feed-forward may instead leave several rows per token to be added (``forward`` returning
+    ``(rows, count)``), which the same kernel sums in a fixed order."""
+
+    roles = {"mixer_norm": NORMS, "mixer": MIXERS, "mixer_out_norm": NORMS}
+    optional_roles = {"ffn_norm": NORMS, "ffn": FEED_FORWARDS, "ffn_out_norm": NORMS}
+    kernels = ("groupnorm",)
+
+    def __init__(self, layer_spec, tensors, dtype, device):
+        self.roles = self._roles_of(layer_spec)
+        super().__init__(layer_spec, tensors, dtype, device)
+        self.hidden = int(layer_spec.params["hidden_size"])
+        self.mult = float(layer_spec.params.get("residual_mult", 1.0))
+        self.has_ffn = "ffn" in layer_spec.parts
+        self.sides = ("mixer", "ffn") if self.has_ffn else ("mixer",)
+        self.gates, self.coefficients = {}, {}
+        for side in self.sides:
+            out_norm = self._parts[f"{side}_out_norm"]
+            if getattr(out_norm, "weight", None) is None or not hasattr(out_norm, "eps") or isinstance(out_norm, LayerNorm):
+                raise UnsupportedError(f"{layer_spec.prefix}: the norm after a sublayer must be an RMS norm")
+            # everything that multiplies the normed output per channel, as one 32-bit vector
+            coefficient = out_norm.weight * self.mult
+            if layer_spec.params.get("layer_scale", False):
+                scale = tensors[f"{layer_spec.part_prefix(side + '_scale')}.weight"]
+                coefficient = coefficient * scale.to(device=device, dtype=torch.float32)
+            self.coefficients[side] = coefficient.contiguous()
+            self.gates[side] = None
+            if layer_spec.params.get("gated", False):
+                prefix = layer_spec.part_prefix(side + "_gate")
+                self.gates[side] = Linear(tensors[f"{prefix}.weight"], dtype, device, bias=tensors[f"{prefix}.bias"])
+                setattr(self, f"{side}_gate", self.gates[side])
+
+    @classmethod
+    def _roles_of(cls, layer_spec):
+        roles = dict(cls.roles)
+        if "ffn" in layer_spec.parts:
+            roles.update(cls.optional_roles)
+        return roles
+
+    @classmethod
+    def schema(cls, layer_spec):
+        schema = {}
+        for role, registry in cls._roles_of(layer_spec).items():
+            part_spec = cls._role_spec(layer_spec, role)
+            schema.update(registry.find(part_spec.kind).schema(part_spec.params, layer_spec.part_prefix(role)))
+        hidden = int(layer_spec.params["hidden_size"])
+        for side in ("mixer", "ffn") if "ffn" in layer_spec.parts else ("mixer",):
+            if layer_spec.params.get("layer_scale", False):
+                schema[f"{layer_spec.part_prefix(side + '_scale')}.weight"] = TensorSpec((hidden,), init="norm", store="float32")
+            if layer_spec.params.get("gated", False):
+                prefix = layer_spec.part_prefix(side + "_gate")
+                schema[f"{prefix}.weight"] = TensorSpec((hidden, hidden))
+                schema[f"{prefix}.bias"] = TensorSpec((hidden,), init="bias")
+        return schema
+
+    @classmethod
+    def cache_request_for(cls, layer_spec):
+        part_spec = cls._role_spec(layer_spec, "mixer")
+        return MIXERS.find(part_spec.kind).cache_request_for(part_spec.params)
+
+    @classmethod
+    def workspace_bytes(cls, layer_spec, tokens, element_bytes):
+        total = tokens * int(layer_spec.params["hidden_size"]) * (8 + element_bytes)   # cleared stream, gate, h
+        for role, registry in cls._roles_of(layer_spec).items():
+            part_spec = cls._role_spec(layer_spec, role)
+            total += registry.find(part_spec.kind).workspace_bytes(part_spec.params, tokens, element_bytes)
+        return total
+
+    def parts(self):
+        # the arrangement itself launches kernels and owns matrices, so it counts among its parts
+        return tuple(self._parts.values()) + (self,)
+
+    def kernel_families(self):
+        names = self.kernels
+        for gate in self.gates.values():
+            if gate is not None:
+                names += gate.kernel_families()
+        return tuple(dict.fromkeys(names))
+
+    def _join(self, ctx, side, h, branch, parts, residual):
+        gate = None
+        if self.gates[side] is not None:
+            gate = ctx.workspace.get("block.gate", (ctx.num_tokens, self.hidden), torch.float32)
+            self.gates[side](ctx, h, epilogue=ops.EPI_STORE, out=gate)
+        out_norm = self._parts[f"{side}_out_norm"]
+        ops.gated_norm_add(branch, parts, gate, self.coefficients[side], residual, out_norm.eps,
+                           int(getattr(out_norm, "groups", 1)))
+
+    def forward(self, ctx, residual, cache, writes_cache):
+        ws = ctx.workspace
+        branch = ws.get("block.branch", (ctx.num_tokens, self.hidden), torch.float32)
+        h = NormedInput(ctx, self.mixer_norm, residual).tensor()
+        branch.zero_()
+        self.mixer.forward(ctx, h, branch, cache, writes_cache)
+        self._join(ctx, "mixer", h, branch, 1, residual)
+        if self.has_ffn:
+            h = NormedInput(ctx, self.ffn_norm, residual).tensor()
+            rows = self.ffn.forward(ctx, h, None) if getattr(self.ffn, "leaves_rows", False) else None
+            if rows is None:
+                branch.zero_()
+                self.ffn.forward(ctx, h, branch)
+                rows = (branch, 1)
+            self._join(ctx, "ffn", h, rows[0], rows[1], residual)
+
+
 BLOCKS.register("prenorm", PreNormBlock)
+BLOCKS.register("sandwich", SandwichBlock)
 BLOCKS.register("outnorm_conv", OutNormConvBlock)
 BLOCKS.register("prenorm_mixer", PreNormMixerBlock)

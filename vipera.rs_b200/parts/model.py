@@ -26,6 +26,8 @@ def model_schema(spec: ModelSpec) -> Schema:
     for layer in spec.layers:
         schema.update(BLOCKS.find(layer.block).schema(layer))
     schema.update(NORMS.find(spec.final_norm.kind).schema(spec.final_norm.params, spec.final_norm_name))
+    if spec.embedding_norm is not None:
+        schema.update(NORMS.find(spec.embedding_norm.kind).schema(spec.embedding_norm.params, spec.embedding_norm_name))
     if spec.head_name is not None:
         schema[spec.head_name] = TensorSpec((spec.vocab_size, spec.hidden_size))
     return schema
@@ -58,6 +60,12 @@ class DecoderModel:
         self.final_norm = norm_cls(spec.final_norm.params, spec.final_norm_name,
                                    fetch(norm_cls.schema(spec.final_norm.params, spec.final_norm_name)),
                                    dtype, self.device)
+        self.embedding_norm = None
+        if spec.embedding_norm is not None:
+            cls = NORMS.find(spec.embedding_norm.kind)
+            self.embedding_norm = cls(spec.embedding_norm.params, spec.embedding_norm_name,
+                                      fetch(cls.schema(spec.embedding_norm.params, spec.embedding_norm_name)),
+                                      dtype, self.device)
         if spec.head_name is None:
             self.head = Linear(self.embedding, dtype, self.device)
         else:
@@ -94,6 +102,8 @@ class DecoderModel:
             for part in block.parts():
                 names.extend(part.kernel_families())
         names.extend(self.final_norm.kernel_families())
+        if self.embedding_norm is not None:
+            names.extend(self.embedding_norm.kernel_families())
         return list(dict.fromkeys(names))
 
     def weight_bytes(self) -> int:
@@ -116,6 +126,9 @@ class DecoderModel:
         ws = ctx.workspace
         residual = ws.get("model.residual", (ctx.num_tokens, self.spec.hidden_size), torch.float32)
         ops.embed(self.embedding, ctx.tokens, residual, self.spec.embedding_scale)
+        if self.embedding_norm is not None:
+            # in place: the normed rows are the stream the first layer reads, in 32-bit
+            self.embedding_norm.forward(ctx, residual, residual)
         for entry in self.spec.schedule:
             self.blocks[entry.layer].forward(ctx, residual, caches.get(entry.cache), entry.writes_cache)
         if ctx.num_logit_rows == 0:

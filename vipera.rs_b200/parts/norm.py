@@ -5,13 +5,17 @@ from __future__ import annotations
 import torch
 
 from ..config.registry import NORMS
+from ..errors import InvalidArgumentError
 from ..kernels import ops
 from ..weights import TensorSpec
 from .base import Norm
 
 
 class RMSNorm(Norm):
-    """params: ``size`` (width of a row), ``eps``.  Tensor: ``<prefix>.weight`` [size]."""
+    """params: ``size`` (width of a row), ``eps`` and, optionally, ``groups`` (the row is cut into
+    that many equal consecutive parts and each part is divided by its own root mean square; default
+    1, the whole row).  Tensor: ``<prefix>.weight`` [size].  The grouped form may write its 32-bit
+    input in place."""
 
     kernels = ("rowwise",)
     fused_kind = "rmsnorm"  # products that can compute a norm on the way recognise it by this
@@ -26,9 +30,19 @@ class RMSNorm(Norm):
         self.eps = float(params["eps"])
         # The weight is used in 32-bit whatever it was stored in (bfloat16 widens exactly).
         self.weight = tensors[f"{prefix}.weight"].to(device=device, dtype=torch.float32).contiguous()
+        self.groups = int(params.get("groups") or 1)
+        if self.size % self.groups:
+            raise InvalidArgumentError(f"{prefix}: {self.groups} groups do not divide a row of {self.size}")
+        if self.groups > 1:
+            # the products that take a norm with them know the norm over whole rows only
+            self.fused_kind = None
+            self.kernels = ("groupnorm",)
 
     def forward(self, ctx, x, out, rows=None):
-        ops.rmsnorm(x, self.weight, out, self.eps, rows)
+        if self.groups > 1:
+            ops.group_rmsnorm(x, self.weight, out, self.eps, self.groups, rows)
+        else:
+            ops.rmsnorm(x, self.weight, out, self.eps, rows)
 
 
 class LayerNorm(Norm):
