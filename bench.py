@@ -651,11 +651,100 @@ def gusolix_decode_bytes(config, batch, history, element=2):
     return {"weights": weights * element, "state": state, "cache": int(cache)}
 
 
+# ---------------------------------------------------------------------------------------
+# --design pugovik: the Pugovik design beside the Qwen2 decoder at equal sizes
+# ---------------------------------------------------------------------------------------
+def pugovik_config(width, heads, kv_heads, ff, layers, vocab, cell_heads, cell_dim, cell_vdim, experts=16, top=4):
+    """`layers` layers in the proportion three of linear attention to one of attention over a cached
+    latent (every second of those reading the pages of the one before it); every layer with a mixture
+    of `experts` gated units of which a token uses `top`, sized so that a token's experts together have
+    the dense inner size; heads of 128 + 64 turning values over a latent of 512."""
+    mlp = {"kind": "moe", "expert": {"ff": ff // top},
+           "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}}}
+    decay = [1.0 - 2.0 ** (-5.0 - 5.0 * index / max(cell_heads - 1, 1)) for index in range(cell_heads)]
+    lightning = {"type": "lightning", "mlp": mlp,
+                 "mixer": {"heads": cell_heads, "dim": cell_dim, "vdim": cell_vdim, "decay": decay}}
+
+    def latent(source=None):
+        mixer = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+                 "rot": {"dims": 64, "base": 10000.0,
+                         "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+        if source is not None:
+            mixer["kv_from"] = source
+        return {"type": "latent_attention", "mlp": mlp, "mixer": mixer}
+
+    order, first = [], None
+    for index in range(layers):
+        if index % 4 != 3:
+            order.append(lightning)
+        elif first is None:
+            order.append(latent())
+            first = index
+        else:
+            order.append(latent(first))
+            first = None
+    return {"architecture": "Pugovik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 4},
+            "residual_mult": 0.5, "layers": order}
+
+
+def pugovik_work(config, tokens, chunk=64):
+    """Floating-point operations of a prompt of `tokens` tokens by class of kernel: products (mixers,
+    gates of the stream, the chosen experts, the output matrix), the linear attention as its chunked
+    form computes it, attention over the latents (scores against rank + rot_dim values, weighted sums
+    of rank values, and the two absorbed matrices per query)."""
+    width = config["width"]
+    flops = {"proj": 2.0 * config["vocab"] * width, "recurrence": 0.0, "attention": 0.0, "experts": 0.0}
+    for layer in config["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "lightning":
+            h, d, dv = m["heads"], m["dim"], m["vdim"]
+            flops["proj"] += 2.0 * tokens * width * (2 * h * d + 3 * h * dv)
+            flops["recurrence"] += 2.0 * tokens * h * (chunk * (d + dv) / 2 + 2 * d * dv)
+        else:
+            h, d, r, dv, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            own = 0 if "kv_from" in m else rank + r
+            flops["proj"] += 2.0 * tokens * width * (h * (d + r) + own + 2 * h * dv)
+            flops["attention"] += 2.0 * tokens * h * ((2 * rank + r) * tokens / 2 + rank * (d + dv))
+        flops["proj"] += 2.0 * tokens * width * width            # the gate of what joins the stream
+        if layer.get("mlp"):
+            router = layer["mlp"]["router"]
+            flops["proj"] += 2.0 * tokens * width * width
+            flops["experts"] += 2.0 * tokens * (router["top"] * 3 * width * layer["mlp"]["expert"]["ff"] + router["experts"] * width)
+    return flops
+
+
+def pugovik_decode_bytes(config, batch, history, element=2):
+    """What one decode step must move: every matrix a token of the batch can use (all experts once the
+    batch's choices cover them: min(experts, batch * top)), states read and written, latents read."""
+    width = config["width"]
+    weights = config["vocab"] * width
+    state = cache = 0
+    for layer in config["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "lightning":
+            h, d, dv = m["heads"], m["dim"], m["vdim"]
+            weights += width * (2 * h * d + 3 * h * dv)
+            state += 2 * batch * h * d * dv * 4
+        else:
+            h, d, r, dv, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            own = 0 if "kv_from" in m else rank + r
+            weights += width * (h * (d + r) + own + 2 * h * dv) + h * rank * (d + dv)
+            cache += batch * history * (rank + r) * element
+        weights += width * width
+        if layer.get("mlp"):
+            router = layer["mlp"]["router"]
+            used = min(router["experts"], batch * router["top"])
+            weights += width * width + used * 3 * width * layer["mlp"]["expert"]["ff"] + router["experts"] * width
+    return {"weights": weights * element, "state": state, "cache": int(cache)}
+
+
 DESIGNS = {
     "nobupel": (lambda *sizes: nobupel_config(*sizes), lambda config, tokens: nobupel_work(config, tokens),
                 lambda config, batch, history: nobupel_decode_bytes(config, batch, history)),
     "gusolix": (lambda *sizes: gusolix_config(*sizes), lambda config, tokens: gusolix_work(config, tokens),
                 lambda config, batch, history: gusolix_decode_bytes(config, batch, history)),
+    "pugovik": (lambda *sizes: pugovik_config(*sizes), lambda config, tokens: pugovik_work(config, tokens),
+                lambda config, batch, history: pugovik_decode_bytes(config, batch, history)),
 }
 
 

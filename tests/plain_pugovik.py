@@ -132,10 +132,33 @@ def route(scores, top, group_count, keep):
     return chosen, torch.gather(scores, 1, chosen)
 
 
-def mixture(h, w, prefix, mlp):
+def route_margin(scores, top, group_count, keep):
+    """Per token, how far the choice is from another one: the smaller of the gap between the last
+    kept group's score and the best dropped one's, and the gap between the last chosen expert's
+    score and the best allowed one left out (infinite where there is no such rival)."""
+    count, experts = scores.shape
+    per_group = experts // group_count
+    grouped = scores.reshape(count, group_count, per_group)
+    group_score = grouped.topk(min(2, per_group), dim=-1).values.sum(-1)
+    margin = torch.full((count,), float("inf"), dtype=scores.dtype)
+    order = group_score.sort(dim=-1, descending=True)
+    if keep < group_count:
+        margin = torch.minimum(margin, order.values[:, keep - 1] - order.values[:, keep])
+    allowed = torch.zeros(count, group_count, dtype=torch.bool)
+    allowed.scatter_(1, order.indices[:, :keep], True)
+    masked = grouped.masked_fill(~allowed[:, :, None], float("-inf")).reshape(count, experts)
+    if top < keep * per_group:
+        ranked = masked.sort(dim=-1, descending=True).values
+        margin = torch.minimum(margin, ranked[:, top - 1] - ranked[:, top])
+    return margin
+
+
+def mixture(h, w, prefix, mlp, margins=None):
     router = mlp["router"]
     scores = torch.sigmoid(h @ w[f"{prefix}.router"].to(F).T)
     chosen, weight = route(scores, int(router["top"]), int(router["groups"]["count"]), int(router["groups"]["keep"]))
+    if margins is not None:
+        margins.append(route_margin(scores, int(router["top"]), int(router["groups"]["count"]), int(router["groups"]["keep"])))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, s in zip(chosen[t].tolist(), weight[t]):
@@ -144,8 +167,9 @@ def mixture(h, w, prefix, mlp):
     return out
 
 
-def forward(config, weights, tokens, return_layers=False):
-    """Logits [T, vocab] of one sequence; with `return_layers` also the stream after every layer."""
+def forward(config, weights, tokens, return_layers=False, margins=None):
+    """Logits [T, vocab] of one sequence; with `return_layers` also the stream after every layer.  A list
+    given as `margins` receives every mixture's route_margin [T]."""
     w = weights
     eps, groups = float(config["norm"]["eps"]), int(config["norm"]["groups"])
     mult = float(config["residual_mult"])
@@ -172,7 +196,7 @@ def forward(config, weights, tokens, return_layers=False):
         x = x + mult * (norm(y, f"{p}.norm1b") * w[f"{p}.ls1"].to(F))
         if layer.get("mlp") is not None:
             h = norm(x, f"{p}.norm2")
-            y = mixture(h, w, f"{p}.mlp", layer["mlp"])
+            y = mixture(h, w, f"{p}.mlp", layer["mlp"], margins)
             y = y * torch.sigmoid(h @ w[f"{p}.rg2"].to(F).T + w[f"{p}.rg2.b"].to(F))
             x = x + mult * (norm(y, f"{p}.norm2b") * w[f"{p}.ls2"].to(F))
         streams.append(x.clone())

@@ -23,7 +23,7 @@ def moe(ff=24, experts=6, top=2, groups=3, keep=2):
 def latent_layer(heads=3, dim=16, rot_dim=8, vdim=24, rank=40, scale=0.3, base=5000.0, scaling=True, kv_from=None, mlp=None):
     rot = {"dims": rot_dim, "base": base}
     if scaling:
-        rot["scaling"] = {"factor": 4.0, "original": 48, "fast": 8.0, "slow": 1.0}
+        rot["scaling"] = {"factor": 4.0, "original": 512, "fast": 4.0, "slow": 0.5}
     mixer = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": rank, "scale": scale, "rot": rot}
     if kv_from is not None:
         mixer["kv_from"] = kv_from
@@ -41,7 +41,7 @@ def config(layers, width=72, vocab=211, eps=3e-6, groups=3, mult=0.8):
 
 # Sizes that share nothing with each other; a layer that reads an earlier layer's latents with other heads.
 MIXED = config([lightning_layer(mlp=moe()),
-                latent_layer(mlp=moe(ff=40, experts=8, top=3, groups=4, keep=3)),
+                latent_layer(mlp=moe(ff=40, experts=9, top=4, groups=3, keep=2)),
                 lightning_layer(heads=2, dim=20, vdim=8, decay=(0.8, 0.99)),
                 latent_layer(heads=5, dim=8, vdim=12, scale=0.5, kv_from=1, mlp=moe(ff=16, experts=4, top=1, groups=2, keep=1))])
 # Sizes the tensor-core products take; a shared cache two layers back.
@@ -51,7 +51,7 @@ WIDE = config([latent_layer(heads=4, dim=64, rot_dim=32, vdim=64, rank=128, scal
                                mlp=moe(ff=64, experts=16, top=4, groups=4, keep=2)),
                latent_layer(heads=2, dim=32, rot_dim=32, vdim=128, rank=128, scale=0.15, base=10000.0, kv_from=0),
                lightning_layer(heads=2, dim=128, vdim=32, decay=(0.95, 0.9999), mlp=moe(ff=256, experts=4, top=2, groups=1, keep=1))],
-              width=256, vocab=512, eps=1e-5, groups=2, mult=0.7)
+              width=256, vocab=640, eps=2e-5, groups=4, mult=0.6)
 # Values the others make equal, even or absent: a width that is no multiple of 8, one norm group, a
 # multiplier of one, one head, groups of one expert, every expert used, one expert in all, a rotated
 # part of two values, no frequency scaling, unrotated size below the rotated one, a decay of one
@@ -73,10 +73,10 @@ CONFIGS = {"mixed": MIXED, "wide": WIDE, "odd": ODD, "latent": ONLY_LATENT, "sha
 
 # How stored tensors are changed (by the end of their names): ("mul", x) or ("add", x).
 SHARP = {".mix.q": ("mul", 25.0), ".mix.dkv": ("mul", 4.0), ".mix.uk": ("mul", 4.0), ".mix.uv": ("mul", 10.0),
-         ".mix.k": ("mul", 20.0), ".mix.v": ("mul", 20.0), ".mlp.router": ("mul", 40.0), ".gate": ("mul", 20.0),
+         ".mix.k": ("mul", 20.0), ".mix.v": ("mul", 20.0), ".mlp.router": ("mul", 8.0), ".gate": ("mul", 20.0),
          ".up": ("mul", 20.0), ".rg1": ("mul", 10.0), ".rg2": ("mul", 10.0)}
 MILD = {".mix.q": ("mul", 10.0), ".mix.uv": ("mul", 10.0), ".mix.k": ("mul", 20.0), ".mix.v": ("mul", 20.0),
-        ".mlp.router": ("mul", 40.0), ".gate": ("mul", 20.0), ".up": ("mul", 20.0), ".rg1": ("mul", 10.0),
+        ".mlp.router": ("mul", 8.0), ".gate": ("mul", 20.0), ".up": ("mul", 20.0), ".rg1": ("mul", 10.0),
         ".rg2": ("mul", 10.0)}
 RULES = {"sharp": SHARP, "mild": MILD, "none": {}}
 
@@ -109,12 +109,24 @@ def read(path: str):
         return json.load(handle), load_file(os.path.join(path, "model.safetensors"))
 
 
-_PLAIN: Dict[tuple, np.ndarray] = {}
+_PLAIN: Dict[tuple, tuple] = {}
 
 
-def plain_logits(path: str, tokens: Sequence[int]) -> np.ndarray:
+def _plain(path: str, tokens: Sequence[int]) -> tuple:
     key = (path, tuple(tokens))
     if key not in _PLAIN:
         config, weights = read(path)
-        _PLAIN[key] = plain.forward(config, weights, list(tokens)).numpy()
+        margins = []
+        logits = plain.forward(config, weights, list(tokens), margins=margins).numpy()
+        least = torch.stack(margins).min(dim=0).values.numpy() if margins else np.full(len(tokens), np.inf)
+        _PLAIN[key] = (logits, least)
     return _PLAIN[key]
+
+
+def plain_logits(path: str, tokens: Sequence[int]) -> np.ndarray:
+    return _plain(path, tokens)[0]
+
+
+def plain_margins(path: str, tokens: Sequence[int]) -> np.ndarray:
+    """Per position, the least margin of any mixture's choice of experts (plain.route_margin)."""
+    return _plain(path, tokens)[1]
