@@ -353,18 +353,26 @@ def test_generate_from_the_command_line():
         assert float(row.max() - row[token]) <= 1e-4 * float(np.abs(row).max()), (index, token)
 
 
+# tokens, hidden, inner size, experts, groups, kept groups, top: many experts in groups, more rows per
+# expert than a tile holds, sizes that are no multiples of the tiles; a few tokens (tiles of 8 rows,
+# an expert with more than 8); sizes the grouped tensor-core products take, experts with no row,
+# with a few and with more than 128
+MIXTURES = {"ragged": (301, 72, 44, 64, 8, 3, 6), "few": (9, 72, 44, 4, 2, 1, 2), "few_odd": (5, 37, 13, 6, 3, 2, 3),
+            "wide": (700, 128, 96, 10, 5, 2, 3), "wide_short": (40, 64, 160, 16, 4, 2, 4)}
+
+
 @pytest.mark.parametrize("score,renormalize,group_top", [("sigmoid", False, 2), ("softmax", True, 1)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_the_mixture_alone(dtype, score, renormalize, group_top):
-    """The mixture's kernels on their own: many experts in groups, more rows per expert than a tile
-    holds, sizes that are no multiples of the tiles; chosen experts, weights and outputs against a
-    plain computation in 64-bit."""
+@pytest.mark.parametrize("sizes", sorted(MIXTURES))
+def test_the_mixture_alone(sizes, dtype, score, renormalize, group_top):
+    """The mixture's kernels on their own, in each of their forms: chosen experts, weights and
+    outputs against a plain computation in 64-bit."""
     import torch
 
     import vipera_rs_b200  # noqa: F401
     from vipera_rs_b200.kernels import ops
 
-    tokens, hidden, ff, experts, groups, keep, top = 301, 72, 44, 64, 8, 3, 6
+    tokens, hidden, ff, experts, groups, keep, top = MIXTURES[sizes]
     generator = torch.Generator().manual_seed(11)
     run = torch.float32 if dtype == "float32" else torch.bfloat16
     h = torch.randn(tokens, hidden, generator=generator).to(run)
@@ -394,12 +402,24 @@ def test_the_mixture_alone(dtype, score, renormalize, group_top):
     device = "cuda:0"
     chosen = torch.empty(tokens, top, dtype=torch.int32, device=device)
     weight = torch.empty(tokens, top, dtype=torch.float32, device=device)
-    scratch = torch.empty(2 * tokens * top + 1 + 3 * ops.moe_max_tiles(tokens, top, experts), dtype=torch.int32, device=device)
-    act = torch.full((tokens * top, ff), float("nan"), dtype=run, device=device)
+    scratch = torch.empty(ops.moe_scratch_words(tokens, top, experts), dtype=torch.int32, device=device)
+    capacity = ops.moe_capacity(tokens, top, experts)
+    act = torch.full((capacity, ff), float("nan"), dtype=run, device=device)
     rows = torch.full((tokens, top * hidden), float("nan"), dtype=torch.float32, device=device)
-    ops.moe(h.to(device), router=router.to(device), gate=gate.to(device), up=up.to(device), down=down.to(device), top=top,
-            groups=groups, keep=keep, group_top=group_top, softmax_scores=score == "softmax", renormalize=renormalize,
-            activation=ops.ACT_SILU, chosen=chosen, weight=weight, scratch=scratch, act=act, rows=rows)
+    xs = torch.full((capacity, hidden), float("nan"), dtype=run, device=device)
+    ys = torch.full((capacity, hidden), float("nan"), dtype=torch.float32, device=device)
+    gate_group = 16 if dtype == "bfloat16" and ff % 16 == 0 else ff
+    gate_up = torch.stack([gate.view(experts, ff // gate_group, gate_group, hidden),
+                           up.view(experts, ff // gate_group, gate_group, hidden)], dim=2).reshape(experts, 2 * ff, hidden)
+    tile_rows, padded = ops.moe_form(tokens, top, hidden, ff, gate_group, run)
+    assert (tile_rows, padded) == {"ragged": (32, False), "few": (8, False), "few_odd": (8, False),
+                                   "wide": (128, True) if dtype == "bfloat16" else (32, False),
+                                   "wide_short": (128, True) if dtype == "bfloat16" else (32, False)}[sizes]
+    ops.moe(h.to(device), router=router.to(device), gate_up=gate_up.contiguous().to(device), down=down.to(device),
+            gate_group=gate_group, top=top, groups=groups, keep=keep, group_top=group_top, softmax_scores=score == "softmax",
+            renormalize=renormalize, activation=ops.ACT_SILU, chosen=chosen, weight=weight, scratch=scratch, act=act,
+            rows=rows, xs=xs, ys=ys)
+    ops.check_kernel_status(torch.device(device))
     got_chosen, got_weight = chosen.cpu().long(), weight.cpu().double()
     # scores that lie within rounding of each other may change places; everything else must agree
     close = (masked.topk(top + 1, dim=-1).values.diff(dim=-1).abs().min(-1).values < 1e-5)

@@ -93,6 +93,11 @@ struct GemmParams {
   __nv_bfloat16* q_out;      // [T, heads * d]
   __nv_bfloat16* k_pool;     // [pages, page_size, kv_heads, d]
   __nv_bfloat16* v_pool;
+  // Grouped product (tokens on the 128-row side, whole tiles, blocks alone): W holds `groups`
+  // matrices [N, K] one after the other, and the 128 tokens of tile tx use matrix tile_group[tx].
+  // The table is written by a kernel ahead of this one, so no weight tile is fetched before it.
+  const int* tile_group;     // [tiles_x] or null
+  int group_stride;          // rows of W from one matrix to the next (N)
 };
 
 // ---------------------------------------------------------------------------------------
@@ -519,7 +524,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       const uint32_t pair_full = PAIR ? in_block(smem_u32(&full[0]), 0) : 0u;   // + 8 * stage
       const int y_row = PAIR ? static_cast<int>(rank) * (BN / 2) : 0;           // this block's rows inside the tile's BN
       Piece first;
-      if (WorkLoop<kEven>(p, PAIR).next(first)) {
+      if (p.tile_group == nullptr && WorkLoop<kEven>(p, PAIR).next(first)) {
         const int tx = PAIR ? 2 * (first.tile % p.tiles_x) + static_cast<int>(rank) : first.tile % p.tiles_x;
         const int ty = first.tile / p.tiles_x;
         const int kb_begin = first.kb_begin;
@@ -546,6 +551,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       while (work.next(piece)) {
         const int tx = PAIR ? 2 * (piece.tile % p.tiles_x) + static_cast<int>(rank) : piece.tile % p.tiles_x;
         const int ty = piece.tile / p.tiles_x;
+        const int group_row = (!SWAP && !PAIR && p.tile_group) ? p.tile_group[tx] * p.group_stride : 0;
         for (int kb = piece.kb_begin; kb < piece.kb_end; ++kb, ++issued) {
           if (issued % kProducers != mine) {
             if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -570,7 +576,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status);
             mbar_expect_tx(&full[stage], Config::kStageBytes);
             tma_load_2d(x_tile, &map_x, &full[stage], kb * kBlockK, tx * kTileX);
-            tma_load_2d(y_tile, &map_y, &full[stage], kb * kBlockK, ty * BN);
+            tma_load_2d(y_tile, &map_y, &full[stage], kb * kBlockK, ty * BN + group_row);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -1358,7 +1364,7 @@ constexpr int kShareLeast = 8;      // even shares: k-blocks a block must get at
 constexpr double kShareCost = 4.0;  // what a block's partial sum costs (written, read back, added), in k-blocks of its time
 
 // `even_ok`: the ending can take partial sums of other blocks (the TMA ending of STORE and RESIDUAL).
-static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE, bool even_ok = false) {
+static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE, bool even_ok = false, bool grouped = false) {
   GemmPlan plan{};
   plan.num_k_blocks = (K + kBlockK - 1) / kBlockK;
   // Tokens go on the 128-row side from 192 tokens on.  A matrix wide enough to give half
@@ -1368,7 +1374,7 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
   // SwiGLU ending: 14.1 us against 17.4; at 128 tokens 14.4 against 22.8).
   static const int nonswap_from = std::getenv("VIPERA_GEMM_NONSWAP_FROM") ? std::atoi(std::getenv("VIPERA_GEMM_NONSWAP_FROM")) : 33;
   plan.swap = true;
-  if (T >= 128 + 64 || (T >= nonswap_from && N >= 64 * sms)) {
+  if (grouped || T >= 128 + 64 || (T >= nonswap_from && N >= 64 * sms)) {
     plan.swap = false;
     plan.tiles_x = (T + kTileX - 1) / kTileX;
     // The widest tile that keeps the SMs busy: a tile of 256 columns reads the least per
@@ -1449,7 +1455,7 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
     static const bool narrow_swaps = std::getenv("VIPERA_GEMM_NARROW_NONSWAP") == nullptr;
     const bool forced = (plan.pair && pair_mode() > 1);   // tests ask for pairs on small sizes too
     const int at_once = plan.pair ? std::max(1, pair_clusters_for(plan.bn)) : sms;
-    if (narrow_swaps && !plan.even_shares && !forced && epilogue != EPI_ROPE_CACHE && plan.tiles_x * plan.tiles_y <= at_once) {
+    if (narrow_swaps && !grouped && !plan.even_shares && !forced && epilogue != EPI_ROPE_CACHE && plan.tiles_x * plan.tiles_y <= at_once) {
       const double this_form = 5.0 + plan.num_k_blocks * 0.3;
       const int bn_other = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
       const int tiles_other = ((N + kTileX - 1) / kTileX) * ((T + bn_other - 1) / bn_other);
@@ -1583,8 +1589,10 @@ static int launch_pairs(const CUtensorMap& map_x, const CUtensorMap& map_y, cons
 // `rope`: for EPI_ROPE_CACHE, the fields of that ending (the others are filled in here).
 static int run_gemm(const void* A, const void* W, int T, int N, int K, int epilogue, const float* bias, void* out,
                     int out_dtype, float* resid, float* scratch, size_t scratch_bytes, int* status, void* stream,
-                    const GemmParams* rope, int activation = ACT_SILU) {
+                    const GemmParams* rope, int activation = ACT_SILU, const int* tile_group = nullptr, int groups = 1) {
   if (T <= 0) return VIPERA_OK;
+  const bool grouped = tile_group != nullptr;
+  if (grouped && (groups <= 0 || T % kTileX != 0 || rope != nullptr || epilogue == EPI_RESIDUAL)) return VIPERA_BAD_ARGUMENT;
   if (N <= 0 || K <= 0 || (K % 8) != 0) return VIPERA_BAD_SHAPE;
   if (epilogue == EPI_SWIGLU && (N % 32) != 0) return VIPERA_BAD_SHAPE;
   if (out_dtype != VIPERA_F32 && out_dtype != VIPERA_BF16) return VIPERA_BAD_DTYPE;
@@ -1594,15 +1602,15 @@ static int run_gemm(const void* A, const void* W, int T, int N, int K, int epilo
   const int sms = sm_count();
   // what the TMA ending of STORE and RESIDUAL needs (the only ending that takes other blocks' partial sums)
   const bool direct_store = std::getenv("VIPERA_GEMM_DIRECT_STORE") != nullptr;
-  const bool even_ok = !direct_store && N % 4 == 0 && scratch != nullptr &&
+  const bool even_ok = !grouped && !direct_store && N % 4 == 0 && scratch != nullptr &&
       ((epilogue == EPI_STORE && out_dtype == VIPERA_F32 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) ||
        (epilogue == EPI_RESIDUAL && (reinterpret_cast<uintptr_t>(resid) & 15) == 0));
   // A bias outside the plain store, or the gated unit's other activation: the instances that know
   // them exist for blocks alone with whole tiles or splits (no pairs, no even shares).
   const bool ext = rope == nullptr && (activation != ACT_SILU || (bias != nullptr && epilogue != EPI_STORE));
   const int pairs_before = pair_mode();
-  if (ext) pair_mode() = 0;
-  const GemmPlan plan = make_plan(T, N, K, sms, epilogue, even_ok && !ext);
+  if (ext || grouped) pair_mode() = 0;
+  const GemmPlan plan = make_plan(T, N, K, sms, epilogue, even_ok && !ext, grouped);
   pair_mode() = pairs_before;
   if (plan.splits > 1 || plan.even_shares) {
     if (!scratch || scratch_bytes < plan.scratch_floats * sizeof(float)) return VIPERA_BAD_ARGUMENT;
@@ -1614,10 +1622,12 @@ static int run_gemm(const void* A, const void* W, int T, int N, int K, int epilo
     if ((r = make_map(&map_y, A, T, K, plan.bn)) != VIPERA_OK) return r;
   } else {
     if ((r = make_map(&map_x, A, T, K, kTileX)) != VIPERA_OK) return r;
-    if ((r = make_map(&map_y, W, N, K, plan.pair ? plan.bn / 2 : plan.bn)) != VIPERA_OK) return r;
+    if ((r = make_map(&map_y, W, grouped ? groups * N : N, K, plan.pair ? plan.bn / 2 : plan.bn)) != VIPERA_OK) return r;
   }
   GemmParams p{};
   if (rope) p = *rope;
+  p.tile_group = tile_group;
+  p.group_stride = N;
   p.tokens = T;
   p.features = N;
   p.num_k_blocks = plan.num_k_blocks;
@@ -1722,6 +1732,18 @@ VIPERA_API int vipera_gemm_tc_act(const void* A, const void* W, int T, int N, in
   if (activation != ACT_SILU && activation != ACT_GELU_TANH) return VIPERA_BAD_ARGUMENT;
   return run_gemm(A, W, T, N, K, epilogue, bias, out, out_dtype, resid, scratch, scratch_bytes, status, stream, nullptr,
                   activation);
+}
+
+// Grouped: W is [groups, N, K]; A is [T, K] with T a multiple of 128, and rows 128 * i .. 128 * i + 127
+// are multiplied by matrix tile_group[i] (a device table that a kernel ahead in the stream writes).
+// Endings STORE and the gated unit.
+VIPERA_API int vipera_gemm_tc_grouped(const void* A, const void* W, int T, int N, int K, int groups, const int* tile_group,
+                                      int epilogue, void* out, int out_dtype, int activation, int* status, void* stream) {
+  if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) return VIPERA_BAD_ARGUMENT;
+  if (activation != ACT_SILU && activation != ACT_GELU_TANH) return VIPERA_BAD_ARGUMENT;
+  if (!tile_group) return VIPERA_BAD_ARGUMENT;
+  return run_gemm(A, W, T, N, K, epilogue, nullptr, out, out_dtype, nullptr, nullptr, 0, status, stream, nullptr, activation,
+                  tile_group, groups);
 }
 
 // What the q/k/v ending needs beside the product itself (mirrored by the caller).

@@ -9,34 +9,55 @@
 //
 // Assignment a = token * top + place.  moe_group_kernel sorts the assignments by expert (one
 // block; the order within an expert does not matter: a row of a product depends on no other
-// row) and cuts each expert's run into tiles of kTileRows rows.  The product kernels run one
-// block per (tile, 64 output columns); blocks past the step's count of tiles leave at once, so
-// the grid depends on the step's size class only.  Every row's sums run over the inner size in
-// a fixed order.  The down product leaves w_e * (its row) in rows[a, :] (32-bit): the sum over
-// a token's places is taken by whoever adds the rows into the stream, in the order of the places.
+// row) and cuts each expert's run into tiles of `tile_rows` rows.  Three forms of the products:
+//   * few assignments (decode): tiles of 8 rows; a warp streams four weight rows once for all rows
+//     of the tile (moe_skinny_kernel), so the step reads each used expert's matrices once;
+//   * many assignments in bfloat16: every expert's run starts at a multiple of 128 sorted rows
+//     (`padded`), the tokens' rows are gathered in that order, and the two products are grouped
+//     products on the tensor cores (gemm_tc.cu: the 128 rows of a tile use the matrices of the
+//     tile's expert); a last kernel weights each row and puts it at its assignment's place;
+//   * otherwise (32-bit, sizes the tensor-core product refuses): tiles of 32 rows on the CUDA cores.
+// Blocks past the step's count of tiles leave at once, so a grid depends on the step's size only.
+// Every row's sums run over the inner size in an order that depends on the form alone.  The down
+// product leaves w_e * (its row) in rows[a, :] (32-bit): the sum over a token's places is taken
+// by whoever adds the rows into the stream, in the order of the places.
+//
+// Gate and up matrices are one tensor [experts, 2 ff, hidden]: `gate_group` gate rows, then the
+// up rows of the same features, and so on (16 for the tensor-core ending; ff: all gate rows first).
 #include "common.cuh"
 
 constexpr int kTileRows = 32;
 constexpr int kTileCols = 64;
 constexpr int kTileInner = 32;
 constexpr int kMaxExperts = 1024;
+constexpr int kSkinnyRows = 8;
+constexpr int kRouteThreads = 256;
 
 struct MoeParams {
   const void* h;            // [tokens, hidden], the run's type
   const float* router;      // [experts, hidden]
-  const void* gate;         // [experts, ff, hidden]
-  const void* up;           // [experts, ff, hidden]
+  const void* gate_up;      // [experts, 2 ff, hidden]
   const void* down;         // [experts, hidden, ff]
   int* chosen;              // [tokens * top]
   float* weight;            // [tokens * top]
-  int* order;               // [tokens * top] assignments sorted by expert
-  int* rank;                // [tokens * top] scratch
+  int* order;               // [capacity] sorted place -> assignment (-1: a place that pads a run)
+  int* rank;                // [tokens * top] assignment -> sorted place
   int* tiles;               // [1 + 3 * max_tiles]: count, then (expert, first sorted place, rows) per tile
-  void* act;                // [tokens * top, ff], the run's type, in sorted order
+  int* tile_expert;         // [max_tiles] the tile's expert (0 past the count)
+  void* act;                // [capacity, ff], the run's type, in sorted order
   float* rows;              // [tokens * top, hidden]
+  void* xs;                 // padded form: [capacity, hidden] the tokens' rows in sorted order
+  float* ys;                // padded form: [capacity, hidden] the down products in sorted order
   int num_tokens, hidden, ff, experts, top, groups, keep, group_top, max_tiles;
   int softmax_scores, renormalize, activation;
+  int gate_group;           // gate rows and up rows alternate in groups of this many
+  int tile_rows;            // 8, 32 or (padded) 128
+  int padded;               // 1: every expert's run starts at a multiple of tile_rows; capacity = max_tiles * tile_rows
 };
+
+__device__ __forceinline__ size_t gate_row(int feature, int group) {
+  return static_cast<size_t>(feature / group) * 2 * group + feature % group;
+}
 
 // The lane holding the largest value wins; equal values go to the lower index.
 __device__ __forceinline__ void warp_argmax(float& best, int& index) {
@@ -51,28 +72,33 @@ __device__ __forceinline__ void warp_argmax(float& best, int& index) {
   }
 }
 
-// A warp per token.
+// A block per token: its warps share the experts' logits between them (a lane sums every 32nd
+// product, the warp adds the lanes), then the first warp chooses.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kRouteThreads)
 moe_route_kernel(MoeParams p) {
   extern __shared__ float route_shared[];
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + warp;
-  if (t >= p.num_tokens) return;
-  float* score = route_shared + warp * (2 * p.experts + p.groups);
+  const int t = blockIdx.x;
+  float* score = route_shared;
   float* open = score + p.experts;          // the score while the expert may still be chosen, else -inf
   float* group_score = open + p.experts;
+  float* h_s = group_score + p.groups;      // [hidden]
   const T* h = static_cast<const T*>(p.h) + static_cast<size_t>(t) * p.hidden;
-  for (int e = 0; e < p.experts; ++e) {
+  for (int i = threadIdx.x; i < p.hidden; i += kRouteThreads) h_s[i] = to_float<T>(h[i]);
+  __syncthreads();
+  for (int e = warp; e < p.experts; e += kRouteThreads / 32) {
     const float* r = p.router + static_cast<size_t>(e) * p.hidden;
     float sum = 0.0f;
-    for (int i = lane; i < p.hidden; i += 32) sum = fmaf(to_float<T>(h[i]), r[i], sum);
+#pragma unroll 4
+    for (int i = lane; i < p.hidden; i += 32) sum = fmaf(h_s[i], r[i], sum);
     sum = warp_sum(sum);
     if (lane == 0) score[e] = sum;
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   if (p.softmax_scores) {
     float top_z = -INFINITY;
     for (int e = lane; e < p.experts; e += 32) top_z = fmaxf(top_z, score[e]);
@@ -156,6 +182,9 @@ moe_group_kernel(MoeParams p) {
   pdl_wait();
   const int assignments = p.num_tokens * p.top;
   for (int e = threadIdx.x; e < p.experts; e += blockDim.x) count[e] = 0;
+  for (int tile = threadIdx.x; tile < p.max_tiles; tile += blockDim.x) p.tile_expert[tile] = 0;
+  if (p.padded)
+    for (int place = threadIdx.x; place < p.max_tiles * p.tile_rows; place += blockDim.x) p.order[place] = -1;
   __syncthreads();
   for (int a = threadIdx.x; a < assignments; a += blockDim.x) p.rank[a] = atomicAdd(&count[p.chosen[a]], 1);
   __syncthreads();
@@ -163,17 +192,167 @@ moe_group_kernel(MoeParams p) {
     int place = 0, tile = 0;
     for (int e = 0; e < p.experts; ++e) {
       start[e] = place;
-      for (int first = 0; first < count[e] && tile < p.max_tiles; first += kTileRows, ++tile) {
+      int first = 0;
+      for (; first < count[e] && tile < p.max_tiles; first += p.tile_rows, ++tile) {
         p.tiles[1 + 3 * tile] = e;
         p.tiles[2 + 3 * tile] = place + first;
-        p.tiles[3 + 3 * tile] = min(kTileRows, count[e] - first);
+        p.tiles[3 + 3 * tile] = min(p.tile_rows, count[e] - first);
+        p.tile_expert[tile] = e;
       }
-      place += count[e];
+      place += p.padded ? first : count[e];
     }
     p.tiles[0] = tile;
   }
   __syncthreads();
-  for (int a = threadIdx.x; a < assignments; a += blockDim.x) p.order[start[p.chosen[a]] + p.rank[a]] = a;
+  for (int a = threadIdx.x; a < assignments; a += blockDim.x) {
+    const int place = start[p.chosen[a]] + p.rank[a];
+    p.rank[a] = place;
+    p.order[place] = a;
+  }
+}
+
+// Padded form: the tokens' rows in sorted order (zero where a place pads a run); a block per place.
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_gather_kernel(MoeParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int place = blockIdx.x;
+  if (place / p.tile_rows >= p.tiles[0]) return;
+  const int a = p.order[place];
+  const int vectors = p.hidden * static_cast<int>(sizeof(T)) / 16;   // the caller sees to whole vectors
+  uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(p.xs) + static_cast<size_t>(place) * p.hidden);
+  if (a < 0) {
+    for (int i = threadIdx.x; i < vectors; i += blockDim.x) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(p.h) + static_cast<size_t>(a / p.top) * p.hidden);
+  for (int i = threadIdx.x; i < vectors; i += blockDim.x) dst[i] = src[i];
+}
+
+// Padded form: rows[a, :] = w_a * ys[sorted place of a, :].
+__global__ void __launch_bounds__(256)
+moe_scatter_kernel(MoeParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int quarter = p.hidden / 4;
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<long long>(p.num_tokens) * p.top * quarter) return;
+  const int a = static_cast<int>(i / quarter), c = static_cast<int>(i % quarter);
+  const float w = p.weight[a];
+  float4 v = reinterpret_cast<const float4*>(p.ys + static_cast<size_t>(p.rank[a]) * p.hidden)[c];
+  v.x *= w, v.y *= w, v.z *= w, v.w *= w;
+  reinterpret_cast<float4*>(p.rows + static_cast<size_t>(a) * p.hidden)[c] = v;
+}
+
+// ---------------------------------------------------------------------------------------
+// Few assignments: a block takes one tile of up to 8 rows and 8 warps x 4 weight rows (GATED: the
+// gate and up rows of 2 features per warp; else 4 output columns per warp).  The tile's rows wait
+// in shared memory; a lane reads 16 bytes of each of its warp's weight rows per turn, so every
+// weight byte is read once per tile, and the lanes' partial sums are added at the end.
+// ---------------------------------------------------------------------------------------
+template <typename T, int VEC>
+__device__ __forceinline__ void load_span(const T* __restrict__ src, float (&dst)[VEC]);
+template <>
+__device__ __forceinline__ void load_span<float, 4>(const float* __restrict__ src, float (&dst)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(src);
+  dst[0] = v.x, dst[1] = v.y, dst[2] = v.z, dst[3] = v.w;
+}
+template <>
+__device__ __forceinline__ void load_span<float, 1>(const float* __restrict__ src, float (&dst)[1]) { dst[0] = src[0]; }
+template <>
+__device__ __forceinline__ void load_span<__nv_bfloat16, 8>(const __nv_bfloat16* __restrict__ src, float (&dst)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(src);
+  const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __bfloat1622float2(pairs[e]);
+    dst[2 * e] = f.x, dst[2 * e + 1] = f.y;
+  }
+}
+template <>
+__device__ __forceinline__ void load_span<__nv_bfloat16, 1>(const __nv_bfloat16* __restrict__ src, float (&dst)[1]) {
+  dst[0] = __bfloat162float(src[0]);
+}
+
+template <typename T, bool GATED, int VEC>
+__global__ void __launch_bounds__(256)
+moe_skinny_kernel(MoeParams p) {
+  extern __shared__ __align__(16) unsigned char skinny_shared[];
+  T* x_s = reinterpret_cast<T*>(skinny_shared);   // [kSkinnyRows][inner]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tile = blockIdx.y;
+  if (tile >= p.tiles[0]) return;
+  const int expert = p.tiles[1 + 3 * tile], first = p.tiles[2 + 3 * tile], rows = p.tiles[3 + 3 * tile];
+  const int inner = GATED ? p.hidden : p.ff;
+  const int outer = GATED ? p.ff : p.hidden;
+  const T* x = static_cast<const T*>(GATED ? p.h : p.act);
+  for (int i = threadIdx.x * VEC; i < rows * inner; i += 256 * VEC) {
+    const int r = i / inner, k = i % inner;   // (inner is a multiple of VEC)
+    const size_t source = GATED ? static_cast<size_t>(p.order[first + r] / p.top) : static_cast<size_t>(first + r);
+    if (VEC > 1) *reinterpret_cast<uint4*>(x_s + i) = *reinterpret_cast<const uint4*>(x + source * inner + k);
+    else x_s[i] = x[source * inner + k];
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // this warp's four weight rows
+  const int per_warp = GATED ? 2 : 4;
+  const int col0 = (blockIdx.x * 8 + warp) * per_warp;
+  if (col0 >= outer) return;
+  const T* w_rows[4];
+  const T* base = static_cast<const T*>(GATED ? p.gate_up : p.down) +
+                  static_cast<size_t>(expert) * (GATED ? 2 : 1) * outer * inner;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int c = min(col0 + (GATED ? j >> 1 : j), outer - 1);
+    const size_t row = GATED ? gate_row(c, p.gate_group) + ((j & 1) ? p.gate_group : 0) : static_cast<size_t>(c);
+    w_rows[j] = base + row * inner;
+  }
+  float acc[4][kSkinnyRows];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int r = 0; r < kSkinnyRows; ++r) acc[j][r] = 0.0f;
+#pragma unroll 2
+  for (int k = lane * VEC; k < inner; k += 32 * VEC) {
+    float w[4][VEC];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) load_span<T, VEC>(w_rows[j] + k, w[j]);
+#pragma unroll
+    for (int r = 0; r < kSkinnyRows; ++r) {
+      if (r < rows) {
+        float xv[VEC];
+        load_span<T, VEC>(x_s + r * inner + k, xv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) acc[j][r] = fmaf(w[j][e], xv[e], acc[j][r]);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int r = 0; r < kSkinnyRows; ++r) acc[j][r] = warp_sum(acc[j][r]);
+  if (lane != 0) return;
+#pragma unroll
+  for (int r = 0; r < kSkinnyRows; ++r) {
+    if (r >= rows) continue;
+    if (GATED) {
+#pragma unroll
+      for (int f = 0; f < 2; ++f)
+        if (col0 + f < outer)
+          static_cast<T*>(p.act)[static_cast<size_t>(first + r) * p.ff + col0 + f] =
+              from_float<T>(gate_activation(acc[2 * f][r], p.activation) * acc[2 * f + 1][r]);
+    } else {
+      const int a = p.order[first + r];
+      const float weight = p.weight[a];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (col0 + j < outer) p.rows[static_cast<size_t>(a) * p.hidden + col0 + j] = weight * acc[j][r];
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -203,8 +382,9 @@ moe_product_kernel(MoeParams p) {
   }
   __syncthreads();
   const T* x = static_cast<const T*>(GATED ? p.h : p.act);
-  const T* w0 = static_cast<const T*>(GATED ? p.gate : p.down) + static_cast<size_t>(expert) * outer * inner;
-  const T* w1 = GATED ? static_cast<const T*>(p.up) + static_cast<size_t>(expert) * outer * inner : nullptr;
+  // GATED: the gate row of feature c is at gate_row(c), its up row gate_group rows further
+  const T* w0 = static_cast<const T*>(GATED ? p.gate_up : p.down) + static_cast<size_t>(expert) * (GATED ? 2 : 1) * outer * inner;
+  const T* w1 = GATED ? w0 + static_cast<size_t>(p.gate_group) * inner : nullptr;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float acc0[2][4], acc1[2][4];
 #pragma unroll
@@ -220,7 +400,7 @@ moe_product_kernel(MoeParams p) {
     for (int i = threadIdx.x; i < kTileCols * kTileInner; i += 256) {
       const int c = i / kTileInner, k = i % kTileInner;
       const bool live = col0 + c < outer && k0 + k < inner;
-      const size_t at = static_cast<size_t>(col0 + c) * inner + k0 + k;
+      const size_t at = (GATED ? gate_row(min(col0 + c, outer - 1), p.gate_group) : static_cast<size_t>(col0 + c)) * inner + k0 + k;
       w_s[0][c][k] = live ? to_float<T>(w0[at]) : 0.0f;
       if (GATED) w_s[1][c][k] = live ? to_float<T>(w1[at]) : 0.0f;
     }
@@ -261,36 +441,106 @@ moe_product_kernel(MoeParams p) {
   }
 }
 
+template <typename T, bool GATED>
+static int launch_skinny(const MoeParams& p, cudaStream_t s) {
+  constexpr int kVec = 16 / static_cast<int>(sizeof(T));
+  const int inner = GATED ? p.hidden : p.ff;
+  const int outer = GATED ? p.ff : p.hidden;
+  const uintptr_t bases = reinterpret_cast<uintptr_t>(GATED ? p.h : p.act) | reinterpret_cast<uintptr_t>(GATED ? p.gate_up : p.down);
+  const bool whole = inner % kVec == 0 && (bases & 15) == 0;
+  const size_t shared = static_cast<size_t>(kSkinnyRows) * inner * sizeof(T);
+  const dim3 grid((outer + (GATED ? 16 : 32) - 1) / (GATED ? 16 : 32), p.max_tiles);
+  if (whole) {
+    static bool configured = false;
+    if (!configured) {
+      if (cudaFuncSetAttribute(moe_skinny_kernel<T, GATED, kVec>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+        return VIPERA_BAD_ARGUMENT;
+      configured = true;
+    }
+    return vipera_launch(moe_skinny_kernel<T, GATED, kVec>, grid, 256, shared, s, p);
+  }
+  static bool configured_single = false;
+  if (!configured_single) {
+    if (cudaFuncSetAttribute(moe_skinny_kernel<T, GATED, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+      return VIPERA_BAD_ARGUMENT;
+    configured_single = true;
+  }
+  return vipera_launch(moe_skinny_kernel<T, GATED, 1>, grid, 256, shared, s, p);
+}
+
+// The router, the grouping and (padded form) the gathered rows.
 template <typename T>
-static int launch_moe(const MoeParams& p, cudaStream_t s) {
-  const size_t route_shared = 4 * static_cast<size_t>(2 * p.experts + p.groups) * sizeof(float);
-  int status = vipera_launch(moe_route_kernel<T>, (p.num_tokens + 3) / 4, 128, route_shared, s, p);
+static int launch_route(const MoeParams& p, cudaStream_t s) {
+  const size_t route_shared = static_cast<size_t>(2 * p.experts + p.groups + p.hidden) * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(moe_route_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+      return VIPERA_BAD_ARGUMENT;
+    configured = true;
+  }
+  int status = vipera_launch(moe_route_kernel<T>, p.num_tokens, kRouteThreads, route_shared, s, p);
   if (status) return status;
   status = vipera_launch(moe_group_kernel, 1, 1024, 0, s, p);
-  if (status) return status;
-  status = vipera_launch(moe_product_kernel<T, true>, dim3((p.ff + kTileCols - 1) / kTileCols, p.max_tiles), 256, 0, s, p);
+  if (status || !p.padded) return status;
+  return vipera_launch(moe_gather_kernel<T>, p.max_tiles * p.tile_rows, 128, 0, s, p);
+}
+
+template <typename T>
+static int launch_products(const MoeParams& p, cudaStream_t s) {
+  if (p.tile_rows == kSkinnyRows) {
+    const int status = launch_skinny<T, true>(p, s);
+    return status ? status : launch_skinny<T, false>(p, s);
+  }
+  int status = vipera_launch(moe_product_kernel<T, true>, dim3((p.ff + kTileCols - 1) / kTileCols, p.max_tiles), 256, 0, s, p);
   if (status) return status;
   return vipera_launch(moe_product_kernel<T, false>, dim3((p.hidden + kTileCols - 1) / kTileCols, p.max_tiles), 256, 0, s, p);
 }
 
-// dtype: the type of h, the experts' matrices and the scratch `act`.
+static int check_moe(const MoeParams& p) {
+  if (p.experts <= 0 || p.experts > kMaxExperts || p.groups <= 0 || p.experts % p.groups || p.keep <= 0 ||
+      p.keep > p.groups || p.top <= 0 || p.top > p.keep * (p.experts / p.groups) || p.group_top < 1 || p.group_top > 2 ||
+      p.hidden <= 0 || p.ff <= 0 || p.gate_group <= 0 || p.ff % p.gate_group)
+    return VIPERA_BAD_SHAPE;
+  if (p.padded ? p.tile_rows != 128 : (p.tile_rows != kSkinnyRows && p.tile_rows != kTileRows)) return VIPERA_BAD_ARGUMENT;
+  if (p.max_tiles < p.num_tokens * p.top / p.tile_rows + min(p.experts, p.num_tokens * p.top) || p.max_tiles > 65535)
+    return VIPERA_BAD_ARGUMENT;
+  if (static_cast<size_t>(2 * p.experts + p.groups + p.hidden) * sizeof(float) > 200 * 1024) return VIPERA_BAD_SHAPE;
+  if (p.tile_rows == kSkinnyRows && static_cast<size_t>(kSkinnyRows) * max(p.hidden, p.ff) * 4 > 200 * 1024) return VIPERA_BAD_SHAPE;
+  if (p.padded && (!p.xs || !p.ys || (p.hidden * 2) % 16 || (reinterpret_cast<uintptr_t>(p.xs) & 15) ||
+                   (reinterpret_cast<uintptr_t>(p.h) & 15) || (reinterpret_cast<uintptr_t>(p.ys) & 15) ||
+                   (reinterpret_cast<uintptr_t>(p.rows) & 15)))
+    return VIPERA_BAD_ARGUMENT;
+  return VIPERA_OK;
+}
+
+// Router and grouping; unless `padded`, the products too.  dtype: the type of h, the experts'
+// matrices and the scratch `act`.  (Padded form: the caller runs the two grouped products on
+// xs and act between this and vipera_moe_scatter.)
 VIPERA_API int vipera_moe(const MoeParams* params, int dtype, void* stream) {
   const MoeParams& p = *params;
   if (p.num_tokens <= 0) return VIPERA_OK;
-  if (p.experts <= 0 || p.experts > kMaxExperts || p.groups <= 0 || p.experts % p.groups || p.keep <= 0 ||
-      p.keep > p.groups || p.top <= 0 || p.top > p.keep * (p.experts / p.groups) || p.group_top < 1 || p.group_top > 2 ||
-      p.hidden <= 0 || p.ff <= 0)
-    return VIPERA_BAD_SHAPE;
-  if (p.max_tiles < p.num_tokens * p.top / kTileRows + min(p.experts, p.num_tokens * p.top) || p.max_tiles > 65535)
-    return VIPERA_BAD_ARGUMENT;
+  int status = check_moe(p);
+  if (status) return status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == VIPERA_F32) return launch_moe<float>(p, s);
-  if (dtype == VIPERA_BF16) return launch_moe<__nv_bfloat16>(p, s);
-  return VIPERA_BAD_DTYPE;
+  if (dtype == VIPERA_F32) {
+    if (p.padded) return VIPERA_BAD_DTYPE;
+    status = launch_route<float>(p, s);
+    return status ? status : launch_products<float>(p, s);
+  }
+  if (dtype != VIPERA_BF16) return VIPERA_BAD_DTYPE;
+  status = launch_route<__nv_bfloat16>(p, s);
+  return (status || p.padded) ? status : launch_products<__nv_bfloat16>(p, s);
+}
+
+VIPERA_API int vipera_moe_scatter(const MoeParams* params, void* stream) {
+  const MoeParams& p = *params;
+  if (p.num_tokens <= 0) return VIPERA_OK;
+  if (!p.padded || p.hidden % 4) return VIPERA_BAD_ARGUMENT;
+  const long long count = static_cast<long long>(p.num_tokens) * p.top * (p.hidden / 4);
+  return vipera_launch(moe_scatter_kernel, static_cast<unsigned>((count + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream), p);
 }
 
 VIPERA_API int vipera_moe_params_size() { return static_cast<int>(sizeof(MoeParams)); }
-VIPERA_API int vipera_moe_tile_rows() { return kTileRows; }
 VIPERA_API const char* vipera_moe_status_text(int status) { return vipera_status_text(status); }
 
 // target[t, :] += sum over the places of rows[t, place, :], in the order of the places.

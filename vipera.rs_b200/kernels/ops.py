@@ -1546,55 +1546,124 @@ def lightning(proj: torch.Tensor, *, offsets, heads: int, dim: int, vdim: int, d
 # ----------------------------------------------------------------------------------------
 class _MoeParams(ctypes.Structure):
     _fields_ = [
-        ("h", _c_void), ("router", _c_void), ("gate", _c_void), ("up", _c_void), ("down", _c_void),
+        ("h", _c_void), ("router", _c_void), ("gate_up", _c_void), ("down", _c_void),
         ("chosen", _c_void), ("weight", _c_void), ("order", _c_void), ("rank", _c_void), ("tiles", _c_void),
-        ("act", _c_void), ("rows", _c_void),
+        ("tile_expert", _c_void), ("act", _c_void), ("rows", _c_void), ("xs", _c_void), ("ys", _c_void),
         ("num_tokens", _c_int), ("hidden", _c_int), ("ff", _c_int), ("experts", _c_int), ("top", _c_int),
         ("groups", _c_int), ("keep", _c_int), ("group_top", _c_int), ("max_tiles", _c_int),
         ("softmax_scores", _c_int), ("renormalize", _c_int), ("activation", _c_int),
+        ("gate_group", _c_int), ("tile_rows", _c_int), ("padded", _c_int),
     ]
 
 
-MOE_TILE_ROWS = 32   # kTileRows in moe.cu
+MOE_SKINNY_ROWS, MOE_PLAIN_ROWS, MOE_GROUPED_ROWS = 8, 32, 128   # kSkinnyRows, kTileRows in moe.cu; kTileX in gemm_tc.cu
+MOE_SKINNY_MOST = int(os.environ.get("VIPERA_MOE_SKINNY_MOST", 64))   # assignments up to which a step takes the 8-row tiles
+MOE_GATE_GROUP = 16   # gate and up rows alternate in groups of this many where the tensor-core ending is to read them
 
 
-def moe_max_tiles(tokens: int, top: int, experts: int) -> int:
-    """The most tiles of assignments a step of `tokens` tokens has."""
-    return tokens * top // MOE_TILE_ROWS + min(experts, tokens * top)
+def moe_form(tokens: int, top: int, hidden: int, ff: int, gate_group: int, dtype: torch.dtype):
+    """(rows of a tile, padded) for a step: 8-row tiles on the CUDA cores for few assignments;
+    grouped tensor-core products over runs padded to 128 rows in bfloat16 where the sizes allow
+    (rows that are whole 16-byte vectors, gate and up rows interleaved in sixteens); else 32-row tiles."""
+    if tokens * top <= MOE_SKINNY_MOST and 8 * max(hidden, ff) * 4 <= 200 * 1024:
+        return MOE_SKINNY_ROWS, False
+    if dtype == torch.bfloat16 and hidden % 8 == 0 and ff % 16 == 0 and gate_group == MOE_GATE_GROUP:
+        return MOE_GROUPED_ROWS, True
+    return MOE_PLAIN_ROWS, False
 
 
-def moe(h: torch.Tensor, *, router: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, top: int,
+def moe_max_tiles(tokens: int, top: int, experts: int, tile_rows: int = MOE_SKINNY_ROWS) -> int:
+    """The most tiles of `tile_rows` assignments a step of `tokens` tokens has."""
+    return tokens * top // tile_rows + min(experts, tokens * top)
+
+
+def moe_capacity(tokens: int, top: int, experts: int) -> int:
+    """Sorted places a step can need in any form (runs padded to whole tiles of 128 at most)."""
+    return max(tokens * top, moe_max_tiles(tokens, top, experts, MOE_GROUPED_ROWS) * MOE_GROUPED_ROWS)
+
+
+def moe_scratch_words(tokens: int, top: int, experts: int) -> int:
+    return moe_capacity(tokens, top, experts) + tokens * top + 1 + 4 * moe_max_tiles(tokens, top, experts)
+
+
+def gemm_tc_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, *, epilogue: int, out: torch.Tensor,
+                    activation: int = ACT_SILU, what: str = "gemm_tc") -> None:
+    """a[M, K] (M a multiple of 128) times one of the matrices w[G, N, K], transposed: rows 128 i ..
+    128 i + 127 use matrix tile_group[i] (int32, written on the device ahead of this call).
+    Endings: plain store, or the gated unit over interleaved gate and up rows."""
+    fn = _function("gemm_tc", "vipera_gemm_tc_grouped",
+                   [_c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int, _c_int, _c_void, _c_void])
+    m, k = a.shape
+    groups, n = w.shape[0], w.shape[1]
+    if w.shape[2] != k or m % 128 or tile_group.numel() < m // 128 or k % 8:
+        raise InvalidArgumentError("gemm_tc_grouped: sizes do not match")
+    width = n // 2 if epilogue == EPI_SWIGLU else n
+    if tuple(out.shape) != (m, width):
+        raise InvalidArgumentError(f"gemm_tc_grouped: out must be [{m}, {width}]")
+    state = _tc_buffers(a.device, 0)
+    _check(fn(_gpu(a, "a", torch.bfloat16), _gpu(w, "w", torch.bfloat16), m, n, k, groups,
+              _gpu(tile_group, "tile_group", torch.int32), epilogue, _gpu(out, "out"), dtype_code(out.dtype), int(activation),
+              state["status"].data_ptr(), _stream()), what)
+
+
+def moe(h: torch.Tensor, *, router: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, gate_group: int, top: int,
         groups: int, keep: int, group_top: int, softmax_scores: bool, renormalize: bool, activation: int,
-        chosen: torch.Tensor, weight: torch.Tensor, scratch: torch.Tensor, act: torch.Tensor, rows: torch.Tensor) -> None:
+        chosen: torch.Tensor, weight: torch.Tensor, scratch: torch.Tensor, act: torch.Tensor, rows: torch.Tensor,
+        xs: Optional[torch.Tensor] = None, ys: Optional[torch.Tensor] = None) -> None:
     """A mixture of gated units over a step.  ``h`` [tokens, hidden]; ``router`` float32 [experts,
-    hidden]; ``gate`` and ``up`` [experts, ff, hidden] and ``down`` [experts, hidden, ff] in h's
-    type.  ``chosen`` int32 and ``weight`` float32 [tokens, top] receive each token's experts and
-    their weights; ``rows`` float32 [tokens, top, hidden] receives each chosen expert's weighted
-    output (their sum over ``top`` is the mixture's output).  ``scratch`` int32 of at least 2 *
-    tokens * top + 1 + 3 * moe_max_tiles(...) words; ``act`` [tokens * top, ff] in h's type."""
+    hidden]; ``gate_up`` [experts, 2 ff, hidden] (``gate_group`` gate rows, then the up rows of the
+    same features, and so on) and ``down`` [experts, hidden, ff] in h's type.  ``chosen`` int32 and
+    ``weight`` float32 [tokens, top] receive each token's experts and their weights; ``rows``
+    float32 [tokens, top, hidden] receives each chosen expert's weighted output (their sum over
+    ``top`` is the mixture's output).  ``scratch`` int32 of moe_scratch_words(...) words; ``act``
+    [moe_capacity(...), ff] in h's type; ``xs`` (h's type) and ``ys`` (float32) [moe_capacity(...),
+    hidden] for the form that runs on the tensor cores."""
     fn = _function("moe", "vipera_moe", [ctypes.POINTER(_MoeParams), _c_int, _c_void])
     _check_struct("moe", "vipera_moe_params_size", _MoeParams)
     tokens, hidden = h.shape
-    experts, ff = gate.shape[0], gate.shape[1]
-    if tuple(router.shape) != (experts, hidden) or tuple(gate.shape) != (experts, ff, hidden) or up.shape != gate.shape or \
-            tuple(down.shape) != (experts, hidden, ff) or gate.dtype != h.dtype or up.dtype != h.dtype or down.dtype != h.dtype:
+    experts, ff = gate_up.shape[0], gate_up.shape[1] // 2
+    if tuple(router.shape) != (experts, hidden) or tuple(gate_up.shape) != (experts, 2 * ff, hidden) or \
+            tuple(down.shape) != (experts, hidden, ff) or gate_up.dtype != h.dtype or down.dtype != h.dtype:
         raise InvalidArgumentError("moe: the experts' matrices do not match h and each other")
-    assignments = tokens * int(top)
-    tiles = moe_max_tiles(tokens, int(top), experts)
-    if chosen.numel() < assignments or weight.numel() < assignments or scratch.numel() < 2 * assignments + 1 + 3 * tiles or \
-            act.numel() < assignments * ff or act.dtype != h.dtype or rows.numel() < assignments * hidden:
+    top = int(top)
+    assignments = tokens * top
+    tile_rows, padded = moe_form(tokens, top, hidden, ff, int(gate_group), h.dtype)
+    if padded and (xs is None or ys is None):
+        tile_rows, padded = MOE_PLAIN_ROWS, False
+    tiles = moe_max_tiles(tokens, top, experts, tile_rows)
+    capacity = tiles * tile_rows if padded else assignments
+    if chosen.numel() < assignments or weight.numel() < assignments or scratch.numel() < moe_scratch_words(tokens, top, experts) or \
+            act.numel() < capacity * ff or act.dtype != h.dtype or rows.numel() < assignments * hidden:
         raise InvalidArgumentError("moe: a scratch buffer is too small")
     p = _MoeParams()
     p.h, p.router = _gpu(h, "h"), _gpu(router, "router", torch.float32)
-    p.gate, p.up, p.down = _gpu(gate, "gate"), _gpu(up, "up"), _gpu(down, "down")
+    p.gate_up, p.down = _gpu(gate_up, "gate_up"), _gpu(down, "down")
     p.chosen, p.weight = _gpu(chosen, "chosen", torch.int32), _gpu(weight, "weight", torch.float32)
     base = _gpu(scratch, "scratch", torch.int32)
-    p.order, p.rank, p.tiles = base, base + 4 * assignments, base + 8 * assignments
+    places = moe_capacity(tokens, top, experts)
+    most = moe_max_tiles(tokens, top, experts)
+    p.order, p.rank, p.tiles = base, base + 4 * places, base + 4 * (places + assignments)
+    p.tile_expert = base + 4 * (places + assignments + 1 + 3 * most)
     p.act, p.rows = _gpu(act, "act"), _gpu(rows, "rows", torch.float32)
-    p.num_tokens, p.hidden, p.ff, p.experts, p.top = int(tokens), int(hidden), int(ff), int(experts), int(top)
+    p.num_tokens, p.hidden, p.ff, p.experts, p.top = int(tokens), int(hidden), int(ff), int(experts), top
     p.groups, p.keep, p.group_top, p.max_tiles = int(groups), int(keep), int(group_top), int(tiles)
     p.softmax_scores, p.renormalize, p.activation = int(bool(softmax_scores)), int(bool(renormalize)), int(activation)
-    _check(fn(ctypes.byref(p), dtype_code(h.dtype), _stream()), "moe", kernels=4)
+    p.gate_group, p.tile_rows, p.padded = int(gate_group), int(tile_rows), int(padded)
+    if not padded:
+        _check(fn(ctypes.byref(p), dtype_code(h.dtype), _stream()), "moe", kernels=4)
+        return
+    if xs.numel() < capacity * hidden or ys.numel() < capacity * hidden or xs.dtype != h.dtype:
+        raise InvalidArgumentError("moe: a scratch buffer is too small")
+    p.xs, p.ys = _gpu(xs, "xs"), _gpu(ys, "ys", torch.float32)
+    _check(fn(ctypes.byref(p), dtype_code(h.dtype), _stream()), "moe", kernels=3)
+    tile_expert = scratch[places + assignments + 1 + 3 * most:places + assignments + 1 + 3 * most + tiles]
+    xs_rows = xs.view(-1)[:capacity * hidden].view(capacity, hidden)
+    act_rows = act.view(-1)[:capacity * ff].view(capacity, ff)
+    ys_rows = ys.view(-1)[:capacity * hidden].view(capacity, hidden)
+    gemm_tc_grouped(xs_rows, gate_up, tile_expert, epilogue=EPI_GATED, out=act_rows, activation=activation, what="moe")
+    gemm_tc_grouped(act_rows, down, tile_expert, epilogue=EPI_STORE, out=ys_rows, what="moe")
+    scatter = _function("moe", "vipera_moe_scatter", [ctypes.POINTER(_MoeParams), _c_void])
+    _check(scatter(ctypes.byref(p), _stream()), "moe")
 
 
 def add_rows(rows: torch.Tensor, parts: int, target: torch.Tensor) -> None:

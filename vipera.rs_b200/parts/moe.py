@@ -8,7 +8,10 @@ sum with ``renormalize``): ``y = sum_e w_e D_e (act(G_e h) * (U_e h))``.
 
 The step's (token, expert) assignments are sorted by expert on the device and each expert's run is
 cut into tiles of rows, so that a tile's products read one expert's matrices; the grid depends on
-the step's size only, and the step can be captured in a CUDA graph (``csrc/kernels/moe.cu``).  Each
+the step's size only, and the step can be captured in a CUDA graph (``csrc/kernels/moe.cu``).  A
+step of few assignments streams each used expert's matrices once through tiles of 8 rows; a long
+step in bfloat16 pads every expert's run to whole tiles of 128 rows and runs the two products as
+grouped products on the tensor cores, the gated unit as the first one's ending.  Each
 chosen expert's weighted output stays a 32-bit row of its own: an arrangement that takes rows
 (``leaves_rows``) sums a token's rows in the order of its places; handed a stream, the part sums
 them into it itself.
@@ -32,7 +35,7 @@ class MixtureOfExperts(FeedForward):
     Tensors: ``<prefix>.router.weight`` [experts, hidden] and, per expert k, ``<prefix>.e<k>.<gate|up>.weight``
     [intermediate, hidden] and ``<prefix>.e<k>.<down>.weight`` [hidden, intermediate]."""
 
-    kernels = ("moe",)
+    kernels = ("moe", "gemm_tc")
     leaves_rows = True   # forward(ctx, h, None) returns (rows [tokens, top * hidden] float32, top)
 
     @staticmethod
@@ -53,9 +56,10 @@ class MixtureOfExperts(FeedForward):
     @classmethod
     def workspace_bytes(cls, params, tokens, element_bytes):
         top, experts = int(params["top"]), int(params["experts"])
-        assignments = tokens * top
-        return (assignments * (params["intermediate_size"] * element_bytes + params["hidden_size"] * 4 + 16)
-                + 12 * ops.moe_max_tiles(tokens, top, experts) + 4)
+        hidden, inter = params["hidden_size"], params["intermediate_size"]
+        capacity = ops.moe_capacity(tokens, top, experts)
+        return (capacity * (inter * element_bytes + hidden * (element_bytes + 4)) + tokens * top * (hidden * 4 + 8)
+                + 4 * ops.moe_scratch_words(tokens, top, experts) + 1024)
 
     def __init__(self, params, prefix, tensors, dtype, device):
         super().__init__(params, prefix, tensors, dtype, device)
@@ -84,21 +88,31 @@ class MixtureOfExperts(FeedForward):
             return torch.stack([tensors[f"{prefix}.e{k}.{which}.weight"] for k in range(self.experts)]).to(
                 device=device, dtype=dtype).contiguous()
 
-        self.gate, self.up, self.down = stacked(gate), stacked(up), stacked(down)
+        # gate and up rows in one tensor: interleaved in sixteens where the tensor-core ending can
+        # read them (bfloat16, an inner size of whole sixteens), else all gate rows, then all up rows
+        self.gate_group = ops.MOE_GATE_GROUP if dtype == torch.bfloat16 and self.inter % ops.MOE_GATE_GROUP == 0 else self.inter
+        pieces = self.inter // self.gate_group
+        self.gate_up = torch.stack([stacked(gate).view(self.experts, pieces, self.gate_group, self.hidden),
+                                    stacked(up).view(self.experts, pieces, self.gate_group, self.hidden)],
+                                   dim=2).reshape(self.experts, 2 * self.inter, self.hidden).contiguous()
+        self.down = stacked(down)
 
     def forward(self, ctx, h, residual):
         count, ws = ctx.num_tokens, ctx.workspace
-        assignments = count * self.top
-        tiles = ops.moe_max_tiles(count, self.top, self.experts)
+        capacity = ops.moe_capacity(count, self.top, self.experts)
         chosen = ws.get("moe.chosen", (count, self.top), torch.int32)
         weight = ws.get("moe.weight", (count, self.top), torch.float32)
-        scratch = ws.get("moe.scratch", (2 * assignments + 1 + 3 * tiles,), torch.int32)
-        act = ws.get("moe.act", (assignments, self.inter), ctx.dtype)
+        scratch = ws.get("moe.scratch", (ops.moe_scratch_words(count, self.top, self.experts),), torch.int32)
+        act = ws.get("moe.act", (capacity, self.inter), ctx.dtype)
         rows = ws.get("moe.rows", (count, self.top * self.hidden), torch.float32)
-        ops.moe(h, router=self.router, gate=self.gate, up=self.up, down=self.down, top=self.top, groups=self.groups,
-                keep=self.keep, group_top=self.group_top, softmax_scores=self.softmax_scores,
+        xs = ys = None
+        if ops.moe_form(count, self.top, self.hidden, self.inter, self.gate_group, ctx.dtype)[1]:
+            xs = ws.get("moe.xs", (capacity, self.hidden), ctx.dtype)
+            ys = ws.get("moe.ys", (capacity, self.hidden), torch.float32)
+        ops.moe(h, router=self.router, gate_up=self.gate_up, down=self.down, gate_group=self.gate_group, top=self.top,
+                groups=self.groups, keep=self.keep, group_top=self.group_top, softmax_scores=self.softmax_scores,
                 renormalize=self.renormalize, activation=self.activation, chosen=chosen, weight=weight, scratch=scratch,
-                act=act, rows=rows)
+                act=act, rows=rows, xs=xs, ys=ys)
         if residual is None:
             return rows, self.top
         ops.add_rows(rows, self.top, residual)
