@@ -137,11 +137,14 @@ class TraceBuilder:
         return number
 
 
-def compare(outputs, builder: TraceBuilder, reference: Dict[str, np.ndarray], tolerance: float, what: str, exempt=()):
+def compare(outputs, builder: TraceBuilder, reference: Dict[str, np.ndarray], tolerance: float, what: str, exempt=(),
+            most: float = 1.0):
     """Hold every emitted row to the plain implementation's row at the same request and
     position: max |difference| <= tolerance * max |plain logit| of that request.  Rows named in
-    `exempt` ((request, position) pairs) need only be finite."""
-    worst = 0.0
+    `exempt` ((request, position) pairs) need only be finite.  With `most` below one, that share
+    of the rows must keep the tolerance and the others four times it (a reduced precision whose
+    rounding can tip a discrete choice inside the model at a few positions)."""
+    worst, over, rows_seen = 0.0, 0, 0
     for number, expect in builder.expect.items():
         rows = outputs[number]
         for index, (name, position) in enumerate(expect):
@@ -153,7 +156,12 @@ def compare(outputs, builder: TraceBuilder, reference: Dict[str, np.ndarray], to
             scale = float(np.abs(reference[name]).max())
             error = float(np.abs(got - want).max()) / scale
             worst = max(worst, error)
+            rows_seen += 1
+            if most < 1.0 and tolerance < error <= 4 * tolerance:
+                over += 1
+                continue
             assert error <= tolerance, (
                 f"{what}: step {number}, request {name}, position {position}: "
                 f"relative error {error:.3e} exceeds {tolerance:.1e}")
+    assert over <= (1.0 - most) * rows_seen, f"{what}: {over} of {rows_seen} rows exceed {tolerance:.1e}"
     return worst

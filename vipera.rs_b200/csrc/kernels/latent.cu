@@ -13,7 +13,7 @@
 // so the keys and values of earlier tokens are never expanded.  Scores, softmax, the sums over
 // keys, the latent's norm and the rotation are 32-bit.  Rotation: values (2i, 2i + 1) of the
 // rotated part turn by the angle whose cosine and sine the tables hold at [position, i].
-#include "common.cuh"
+#include "attention_mma.cuh"
 
 constexpr int kMaxRank = 512;   // latent size
 constexpr int kMaxRot = 128;    // rotated part
@@ -79,10 +79,12 @@ latent_absorb_kernel(const float* __restrict__ proj, long long proj_width, int q
   }
   __syncthreads();
   const TW* u = up_k + static_cast<size_t>(h) * d * rank;
-  for (int r = threadIdx.x; r < rank; r += blockDim.x) {
+  // (blocks along z share the rank between them)
+  for (int r = blockIdx.z * blockDim.x + threadIdx.x; r < rank; r += gridDim.z * blockDim.x) {
     float acc[kTile];
 #pragma unroll
     for (int tt = 0; tt < kTile; ++tt) acc[tt] = 0.0f;
+#pragma unroll 8
     for (int e = 0; e < d; ++e) {
       const float w = to_float<TW>(u[static_cast<size_t>(e) * rank + r]);
 #pragma unroll
@@ -92,6 +94,7 @@ latent_absorb_kernel(const float* __restrict__ proj, long long proj_width, int q
     for (int tt = 0; tt < kTile; ++tt)
       if (tt < count) qa[(static_cast<size_t>(t0 + tt) * heads + h) * (rank + rot) + r] = acc[tt] * scale;
   }
+  if (blockIdx.z != 0) return;
   for (int i = threadIdx.x; i < count * (rot / 2); i += blockDim.x) {
     const int tt = i / (rot / 2), pair = i % (rot / 2);
     const int t = t0 + tt;
@@ -217,6 +220,266 @@ latent_attention_kernel(const float* __restrict__ qa, float* __restrict__ mixed,
 }
 
 // ---------------------------------------------------------------------------------------
+// The same fold on the tensor cores (bfloat16 caches; mma.sync m16n8k16, 32-bit accumulation).
+// A block owns 16 query rows, a row being a (token, head): `tokens_per_tile` neighbouring tokens
+// by `head_group` heads, all of one request (a tile that spans several requests is folded once per
+// request, the other requests' rows masked).  Keys come 64 at a time as rows [c | kr] of shared
+// memory, the next tile on its way (cp.async) while this one is used.  Per tile the eight warps
+//   1. each score 8 keys against all 16 rows: S = Q K^T over rank + rot values;
+//   2. each take two rows: running maximum, weights p = exp(s - m) rounded to bfloat16, their sum;
+//   3. each add P C into their 1/8 of the latent's columns.
+// With `num_splits` > 1 a block folds keys [split * split_keys, ...) only and leaves (m, sum,
+// unnormalised columns); latent_combine_kernel joins the splits.  NR: the columns the block's
+// accumulators cover (128, 256 or 512, at least the rank rounded up to 16).
+// ---------------------------------------------------------------------------------------
+constexpr int kFoldRows = 16;
+constexpr int kFoldKeys = 64;
+constexpr int kFoldThreads = 256;
+constexpr int kScoreStride = kFoldKeys + 4;   // floats
+constexpr int kWeightStride = kFoldKeys + 8;  // bf16
+
+struct LatentFoldParams {
+  const float* qa;                 // [tokens, heads, rank + rot]
+  const __nv_bfloat16* k_pool;     // latents
+  const __nv_bfloat16* v_pool;     // rotated key parts
+  const int* token_entry;
+  const int* positions;
+  const int* block_table;
+  float* out;                      // [tokens * heads, rank]
+  float* part;                     // splits: [num_splits][tokens * heads][rank + 2]: columns, then m and sum
+  int num_tokens, heads, rank, rot, table_width, page_size;
+  int head_group, tokens_per_tile, split_keys, num_splits;
+};
+
+__host__ __device__ __forceinline__ int round_up(int v, int to) { return (v + to - 1) / to * to; }
+
+template <int NR>
+__global__ void __launch_bounds__(kFoldThreads)
+latent_fold_kernel(LatentFoldParams p) {
+  extern __shared__ __align__(16) unsigned char fold_shared[];
+  const int rank_pad = round_up(p.rank, 16);
+  const int width_pad = round_up(rank_pad + round_up(p.rot, 16), 32);
+  const int stride = width_pad + 8;   // bf16 per row: rows 16 bytes apart modulo 128, so ldmatrix meets no bank twice
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(fold_shared);
+  __nv_bfloat16* k_s = q_s + kFoldRows * stride;                       // two tiles of kFoldKeys rows
+  float* s_s = reinterpret_cast<float*>(k_s + 2 * kFoldKeys * stride);
+  __nv_bfloat16* p_s = reinterpret_cast<__nv_bfloat16*>(s_s + kFoldRows * kScoreStride);
+  float* m_s = reinterpret_cast<float*>(p_s + kFoldRows * kWeightStride);
+  float* l_s = m_s + kFoldRows;
+  float* alpha_s = l_s + kFoldRows;
+  int* limit_s = reinterpret_cast<int*>(alpha_s + kFoldRows);
+  int* row_s = limit_s + kFoldRows;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  {
+    // everything the copies never write (the columns that pad rank and rot) must read as zero
+    uint4* all = reinterpret_cast<uint4*>(fold_shared);
+    const int vectors = (kFoldRows + 2 * kFoldKeys) * stride * 2 / 16;
+    for (int i = threadIdx.x; i < vectors; i += kFoldThreads) all[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t0 = blockIdx.x * p.tokens_per_tile;
+  const int head0 = blockIdx.y * p.head_group;
+  const int split = blockIdx.z;
+  const int width = p.rank + p.rot;
+  const int rank_chunks = p.rank / 8, row_chunks = rank_chunks + p.rot / 8;
+  const int total_rows = p.num_tokens * p.heads;
+  unsigned done = 0;
+  for (;;) {
+    int lead = -1;
+    for (int tq = 0; tq < p.tokens_per_tile; ++tq)
+      if (t0 + tq < p.num_tokens && !((done >> tq) & 1u)) { lead = tq; break; }
+    if (lead < 0) break;
+    const int entry = p.token_entry[t0 + lead];
+    int last_key = -1;
+    unsigned taken = 0;
+    for (int tq = lead; tq < p.tokens_per_tile && t0 + tq < p.num_tokens; ++tq)
+      if (!((done >> tq) & 1u) && p.token_entry[t0 + tq] == entry) {
+        taken |= 1u << tq;
+        last_key = max(last_key, p.positions[t0 + tq]);
+      }
+    __syncthreads();   // the pass before is done with the rows' tables
+    if (threadIdx.x < kFoldRows) {
+      const int r = threadIdx.x, tq = r / p.head_group, head = head0 + r % p.head_group;
+      const bool valid = tq < p.tokens_per_tile && ((taken >> tq) & 1u) && head < p.heads;
+      limit_s[r] = valid ? p.positions[t0 + tq] : -1;
+      row_s[r] = valid ? (t0 + tq) * p.heads + head : -1;
+      m_s[r] = -INFINITY;
+      l_s[r] = 0.0f;
+    }
+    done |= taken;
+    __syncthreads();
+    for (int i = threadIdx.x; i < kFoldRows * width; i += kFoldThreads) {
+      const int r = i / width, c = i % width;
+      const float v = row_s[r] >= 0 ? p.qa[static_cast<size_t>(row_s[r]) * width + c] : 0.0f;
+      q_s[r * stride + (c < p.rank ? c : rank_pad + c - p.rank)] = __float2bfloat16(v);
+    }
+    const int begin = split * p.split_keys;
+    const int end = min(last_key + 1, begin + p.split_keys);
+    const int num_tiles = end > begin ? (end - begin + kFoldKeys - 1) / kFoldKeys : 0;
+    const int* table = p.block_table + static_cast<size_t>(entry) * p.table_width;
+
+    auto copy_tile = [&](int tile) {
+      __nv_bfloat16* dst_tile = k_s + (tile & 1) * kFoldKeys * stride;
+      const int key0 = begin + tile * kFoldKeys;
+      for (int i = threadIdx.x; i < kFoldKeys * row_chunks; i += kFoldThreads) {
+        const int local = i / row_chunks, chunk = i % row_chunks;
+        const int key = key0 + local;
+        const bool valid = key < end;
+        const __nv_bfloat16* src = p.k_pool;
+        if (valid) {
+          const size_t slot = static_cast<size_t>(table[key / p.page_size]) * p.page_size + key % p.page_size;
+          src = chunk < rank_chunks ? p.k_pool + slot * p.rank + chunk * 8 : p.v_pool + slot * p.rot + (chunk - rank_chunks) * 8;
+        }
+        const int column = chunk < rank_chunks ? chunk * 8 : rank_pad + (chunk - rank_chunks) * 8;
+        cp_async_16(smem_addr(dst_tile + local * stride + column), src, valid);
+      }
+      cp_async_commit();
+    };
+
+    constexpr int kPairs = NR / 8 / 16;   // pairs of 8-column tiles a warp accumulates
+    float acc[2 * kPairs][4];
+#pragma unroll
+    for (int j = 0; j < 2 * kPairs; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[j][e] = 0.0f;
+    const int column0 = warp * (NR / 8);
+    const int g = lane >> 2, pair = (lane & 3) * 2;
+    if (num_tiles > 0) copy_tile(0);
+    for (int tile = 0; tile < num_tiles; ++tile) {
+      cp_async_wait<0>();
+      __syncthreads();   // this tile has landed (and the queries, before the first); the tile before is read out
+      if (tile + 1 < num_tiles) copy_tile(tile + 1);
+      const __nv_bfloat16* keys = k_s + (tile & 1) * kFoldKeys * stride;
+      const int key0 = begin + tile * kFoldKeys;
+      {
+        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const uint32_t k_addr = smem_addr(keys + (warp * 8 + (lane & 7)) * stride + (lane >> 3) * 8);
+        const uint32_t q_addr = smem_addr(q_s + ((lane & 7) + ((lane >> 3) & 1) * 8) * stride + (lane >> 4) * 8);
+        for (int k0 = 0; k0 < width_pad; k0 += 32) {
+          uint32_t b[4], a[4];
+          ldmatrix_x4(b, k_addr + k0 * 2);
+          ldmatrix_x4(a, q_addr + k0 * 2);
+          mma_16816(c, a, b[0], b[1]);
+          ldmatrix_x4(a, q_addr + (k0 + 16) * 2);
+          mma_16816(c, a, b[2], b[3]);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int row = g + (e >> 1) * 8, col = warp * 8 + pair + (e & 1);
+          const int key = key0 + col;
+          s_s[row * kScoreStride + col] = (key <= limit_s[row] && key < end) ? c[e] : -INFINITY;
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int row = warp * 2 + i;
+        const float v0 = s_s[row * kScoreStride + lane], v1 = s_s[row * kScoreStride + lane + 32];
+        const float before = m_s[row];
+        const float top = fmaxf(before, warp_max(fmaxf(v0, v1)));
+        float alpha = 1.0f, w0 = 0.0f, w1 = 0.0f;
+        if (top > -INFINITY) {
+          alpha = expf(before - top);   // 0 while nothing was seen
+          w0 = __bfloat162float(__float2bfloat16(expf(v0 - top)));
+          w1 = __bfloat162float(__float2bfloat16(expf(v1 - top)));
+        }
+        p_s[row * kWeightStride + lane] = __float2bfloat16(w0);
+        p_s[row * kWeightStride + lane + 32] = __float2bfloat16(w1);
+        const float sum = warp_sum(w0 + w1);
+        if (lane == 0) {
+          m_s[row] = top;
+          l_s[row] = l_s[row] * alpha + sum;
+          alpha_s[row] = alpha;
+        }
+      }
+      __syncthreads();
+      {
+        const float alpha0 = alpha_s[g], alpha1 = alpha_s[g + 8];
+#pragma unroll
+        for (int j = 0; j < 2 * kPairs; ++j) {
+          acc[j][0] *= alpha0, acc[j][1] *= alpha0;
+          acc[j][2] *= alpha1, acc[j][3] *= alpha1;
+        }
+        const uint32_t p_addr = smem_addr(p_s + ((lane & 7) + ((lane >> 3) & 1) * 8) * kWeightStride + (lane >> 4) * 8);
+        const uint32_t c_addr = smem_addr(keys + ((lane & 7) + ((lane >> 3) & 1) * 8) * stride + column0 + (lane >> 4) * 8);
+#pragma unroll
+        for (int kk = 0; kk < kFoldKeys / 16; ++kk) {
+          uint32_t a[4];
+          ldmatrix_x4(a, p_addr + kk * 16 * 2);
+#pragma unroll
+          for (int j = 0; j < kPairs; ++j) {
+            if (column0 + 16 * j < rank_pad) {
+              uint32_t b[4];
+              ldmatrix_x4_trans(b, c_addr + (kk * 16 * stride + 16 * j) * 2);
+              mma_16816(acc[2 * j], a, b[0], b[1]);
+              mma_16816(acc[2 * j + 1], a, b[2], b[3]);
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();   // the last sums are written
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int row = g + half * 8;
+      const int out_row = row_s[row];
+      if (out_row < 0) continue;
+      const float total = l_s[row];
+      if (p.num_splits == 1) {
+        const float inverse = 1.0f / total;
+#pragma unroll
+        for (int j = 0; j < 2 * kPairs; ++j) {
+          const int col = column0 + 8 * j + pair;
+          if (col < p.rank) p.out[static_cast<size_t>(out_row) * p.rank + col] = acc[j][2 * half] * inverse;
+          if (col + 1 < p.rank) p.out[static_cast<size_t>(out_row) * p.rank + col + 1] = acc[j][2 * half + 1] * inverse;
+        }
+      } else {
+        float* part = p.part + (static_cast<size_t>(split) * total_rows + out_row) * (p.rank + 2);
+#pragma unroll
+        for (int j = 0; j < 2 * kPairs; ++j) {
+          const int col = column0 + 8 * j + pair;
+          if (col < p.rank) part[col] = acc[j][2 * half];
+          if (col + 1 < p.rank) part[col + 1] = acc[j][2 * half + 1];
+        }
+        if (warp == 0 && pair == 0) {
+          part[p.rank] = m_s[row];
+          part[p.rank + 1] = total;
+        }
+      }
+    }
+  }
+}
+
+// out[row, :] = sum_s e^(m_s - m) columns_s / sum_s e^(m_s - m) sum_s over the splits that saw a key.
+__global__ void __launch_bounds__(128)
+latent_combine_kernel(LatentFoldParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const size_t rows = static_cast<size_t>(p.num_tokens) * p.heads, each = p.rank + 2;
+  float top = -INFINITY;
+  for (int s = 0; s < p.num_splits; ++s) {
+    const float* part = p.part + (s * rows + row) * each;
+    if (part[p.rank + 1] > 0.0f) top = fmaxf(top, part[p.rank]);
+  }
+  float total = 0.0f;
+  for (int s = 0; s < p.num_splits; ++s) {
+    const float* part = p.part + (s * rows + row) * each;
+    if (part[p.rank + 1] > 0.0f) total += part[p.rank + 1] * expf(part[p.rank] - top);
+  }
+  const float inverse = 1.0f / total;
+  for (int c = threadIdx.x; c < p.rank; c += blockDim.x) {
+    float sum = 0.0f;
+    for (int s = 0; s < p.num_splits; ++s) {
+      const float* part = p.part + (s * rows + row) * each;
+      if (part[p.rank + 1] > 0.0f) sum += part[c] * expf(part[p.rank] - top);
+    }
+    p.out[static_cast<size_t>(row) * p.rank + c] = sum * inverse;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // out[t, h * dv + v] = (sum_r l[t, h, r] V[h, r, v]) * sigmoid(gate[t, h * dv + v]).  V is stored
 // transposed per head, [heads, rank, dv], so that neighbouring threads read neighbouring values.
 // `gate` is the pre-activation in `proj` at column g_off (g_off < 0: no gate).
@@ -241,6 +504,7 @@ latent_expand_kernel(const float* __restrict__ latent_out, const TW* __restrict_
     float acc[kTile];
 #pragma unroll
     for (int tt = 0; tt < kTile; ++tt) acc[tt] = 0.0f;
+#pragma unroll 8
     for (int r = 0; r < rank; ++r) {
       const float x = to_float<TW>(w[static_cast<size_t>(r) * dv + v]);
 #pragma unroll
@@ -276,7 +540,75 @@ struct LatentParams {
   void* out;               // [tokens, heads * dv]
   int num_tokens, heads, d, rot, dv, rank, table_width, page_size;
   float scale, eps;
+  float* part;             // scratch of the tensor-core fold's splits: [num_splits][tokens * heads][rank + 2], or null
+  int split_keys, num_splits;   // as vipera_latent_plan gives them (1 split: the whole history in one block)
 };
+
+// How the tensor-core fold cuts a step: {tokens per tile, heads per tile, keys per split, splits}.
+// Few blocks (decode) are cut along the keys, in whole tiles of 64, until the device has some
+// four blocks per SM.
+static void latent_plan(int tokens, int heads, int max_keys, int sms, int* plan) {
+  const int head_group = heads < kFoldRows ? heads : kFoldRows;
+  const int per_tile = kFoldRows / head_group;
+  const long base = static_cast<long>((tokens + per_tile - 1) / per_tile) * ((heads + head_group - 1) / head_group);
+  int bound = kFoldKeys;
+  while (bound < max_keys) bound *= 2;
+  long want = (4L * sms) / base;
+  if (want > bound / kFoldKeys) want = bound / kFoldKeys;
+  if (want > 64) want = 64;
+  if (want < 1) want = 1;
+  int chunk = static_cast<int>((bound + want - 1) / want);
+  chunk = (chunk + kFoldKeys - 1) / kFoldKeys * kFoldKeys;
+  plan[0] = per_tile;
+  plan[1] = head_group;
+  plan[2] = chunk;
+  plan[3] = (bound + chunk - 1) / chunk;
+}
+
+VIPERA_API int vipera_latent_plan(int tokens, int heads, int max_keys, int sms, int* plan) {
+  if (tokens <= 0 || heads <= 0 || sms <= 0) return VIPERA_BAD_ARGUMENT;
+  latent_plan(tokens, heads, max_keys < 1 ? 1 : max_keys, sms, plan);
+  return VIPERA_OK;
+}
+
+template <int NR>
+static int launch_fold(const LatentFoldParams& f, dim3 grid, size_t shared, cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(latent_fold_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024) != cudaSuccess)
+      return VIPERA_BAD_ARGUMENT;
+    configured = true;
+  }
+  return vipera_launch(latent_fold_kernel<NR>, grid, kFoldThreads, shared, s, f);
+}
+
+static int launch_fold_any(const LatentParams& p, cudaStream_t s) {
+  LatentFoldParams f{};
+  f.qa = p.qa;
+  f.k_pool = static_cast<const __nv_bfloat16*>(p.k_pool);
+  f.v_pool = static_cast<const __nv_bfloat16*>(p.v_pool);
+  f.token_entry = p.token_entry;
+  f.positions = p.positions;
+  f.block_table = p.block_table;
+  f.out = p.latent_out;
+  f.part = p.part;
+  f.num_tokens = p.num_tokens, f.heads = p.heads, f.rank = p.rank, f.rot = p.rot;
+  f.table_width = p.table_width, f.page_size = p.page_size;
+  f.head_group = p.heads < kFoldRows ? p.heads : kFoldRows;
+  f.tokens_per_tile = kFoldRows / f.head_group;
+  f.num_splits = p.num_splits > 1 && p.part ? p.num_splits : 1;
+  f.split_keys = f.num_splits > 1 ? p.split_keys : 0x3fffffff;
+  const int rank_pad = round_up(p.rank, 16);
+  const int stride = round_up(rank_pad + round_up(p.rot, 16), 32) + 8;
+  const size_t shared = static_cast<size_t>(kFoldRows + 2 * kFoldKeys) * stride * 2 + kFoldRows * kScoreStride * 4 +
+                        kFoldRows * kWeightStride * 2 + kFoldRows * 5 * 4;
+  const dim3 grid((p.num_tokens + f.tokens_per_tile - 1) / f.tokens_per_tile, (p.heads + f.head_group - 1) / f.head_group,
+                  f.num_splits);
+  int status = rank_pad <= 128 ? launch_fold<128>(f, grid, shared, s)
+             : rank_pad <= 256 ? launch_fold<256>(f, grid, shared, s) : launch_fold<512>(f, grid, shared, s);
+  if (status || f.num_splits == 1) return status;
+  return vipera_launch(latent_combine_kernel, p.num_tokens * p.heads, 128, 0, s, f);
+}
 
 template <typename T>
 static int launch_latent(const LatentParams& p, cudaStream_t s) {
@@ -289,14 +621,20 @@ static int launch_latent(const LatentParams& p, cudaStream_t s) {
     if (status) return status;
   }
   const dim3 tiles((p.num_tokens + kTile - 1) / kTile, p.heads);
-  status = vipera_launch(latent_absorb_kernel<T>, tiles, 128, kTile * p.d * sizeof(float), s, p.proj, p.proj_width, p.q_off,
+  const dim3 absorb_grid(tiles.x, tiles.y, (p.rank + 127) / 128);
+  status = vipera_launch(latent_absorb_kernel<T>, absorb_grid, 128, kTile * p.d * sizeof(float), s, p.proj, p.proj_width, p.q_off,
                          static_cast<const T*>(p.up_k), p.positions, p.cos_table, p.sin_table, p.qa, p.num_tokens,
                          p.heads, p.d, p.rank, p.rot, p.scale);
   if (status) return status;
-  status = vipera_launch(latent_attention_kernel<T>, dim3(p.num_tokens, (p.heads + kWarps - 1) / kWarps), kWarps * 32,
-                         kWarps * (p.rank + p.rot) * sizeof(float), s, p.qa, p.latent_out,
-                         static_cast<const T*>(p.k_pool), static_cast<const T*>(p.v_pool), p.token_entry, p.positions,
-                         p.block_table, p.table_width, p.page_size, p.heads, p.rank, p.rot);
+  // bfloat16 caches whose rows are whole 16-byte pieces fold on the tensor cores
+  if (sizeof(T) == 2 && p.rank % 8 == 0 && p.rot % 8 == 0 && p.num_tokens < (1 << 24) / p.heads &&
+      (p.num_splits <= 1 || p.split_keys % kFoldKeys == 0))
+    status = launch_fold_any(p, s);
+  else
+    status = vipera_launch(latent_attention_kernel<T>, dim3(p.num_tokens, (p.heads + kWarps - 1) / kWarps), kWarps * 32,
+                           kWarps * (p.rank + p.rot) * sizeof(float), s, p.qa, p.latent_out,
+                           static_cast<const T*>(p.k_pool), static_cast<const T*>(p.v_pool), p.token_entry, p.positions,
+                           p.block_table, p.table_width, p.page_size, p.heads, p.rank, p.rot);
   if (status) return status;
   const int threads = p.dv >= 128 ? 128 : (p.dv + 31) / 32 * 32;
   return vipera_launch(latent_expand_kernel<T, T>, tiles, threads, kTile * p.rank * sizeof(float), s, p.latent_out,

@@ -1433,14 +1433,32 @@ class _LatentParams(ctypes.Structure):
         ("qa", _c_void), ("latent_out", _c_void), ("out", _c_void),
         ("num_tokens", _c_int), ("heads", _c_int), ("d", _c_int), ("rot", _c_int), ("dv", _c_int), ("rank", _c_int),
         ("table_width", _c_int), ("page_size", _c_int), ("scale", _c_float), ("eps", _c_float),
+        ("part", _c_void), ("split_keys", _c_int), ("num_splits", _c_int),
     ]
+
+
+@functools.lru_cache(maxsize=4096)
+def latent_plan(tokens: int, heads: int, max_keys: int, sm_count: int):
+    """How the tensor-core fold over the latents cuts a step: (tokens per tile, heads per tile,
+    keys per split, splits)."""
+    fn = _function("latent", "vipera_latent_plan", [_c_int] * 4 + [ctypes.POINTER(_c_int)])
+    plan = (_c_int * 4)()
+    _check(fn(int(tokens), int(heads), int(max_keys), int(sm_count), plan), "latent_plan", kernels=0)
+    return tuple(plan)
+
+
+def latent_part_floats(tokens: int, heads: int, rank: int, max_keys: int, sm_count: int) -> int:
+    """Floats of scratch the fold's splits need for a step (0 when it runs without splits)."""
+    splits = latent_plan(tokens, heads, max_keys, sm_count)[3]
+    return splits * tokens * heads * (rank + 2) if splits > 1 else 0
 
 
 def latent_attention(proj: torch.Tensor, *, q_off: int, g_off: int, kv_off: int, up_k: torch.Tensor, up_v: torch.Tensor,
                      norm_weight: Optional[torch.Tensor], eps: float, positions: torch.Tensor, token_entry: torch.Tensor,
                      block_table: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, k_pool: torch.Tensor,
                      v_pool: torch.Tensor, qa: torch.Tensor, latent_out: torch.Tensor, out: torch.Tensor, heads: int,
-                     head_dim: int, rot_dim: int, value_dim: int, scale: float) -> None:
+                     head_dim: int, rot_dim: int, value_dim: int, scale: float, max_keys: int = 0,
+                     part: Optional[torch.Tensor] = None) -> None:
     """Causal softmax attention whose keys and values are products of a cached latent.  ``proj``
     float32 [tokens, width] holds q (head by head [head_dim | rot_dim]) at column ``q_off``, the
     output gate's pre-activation at ``g_off`` (negative: no gate) and the down projection
@@ -1449,7 +1467,9 @@ def latent_attention(proj: torch.Tensor, *, q_off: int, g_off: int, kv_off: int,
     ``v_pool`` [pages, page_size, 1, rot_dim] the rotated key part the heads share.  ``up_k``
     [heads * head_dim, rank] and ``up_v`` [heads, rank, value_dim] (each head's value matrix
     transposed) are in the pools' type, as is ``out`` [tokens, heads * value_dim]; ``qa`` float32
-    [tokens, heads, rank + rot_dim] and ``latent_out`` float32 [tokens, heads, rank] are scratch."""
+    [tokens, heads, rank + rot_dim] and ``latent_out`` float32 [tokens, heads, rank] are scratch.
+    ``max_keys`` (at least the longest history of the step) and ``part`` (float32,
+    latent_part_floats(...)) let a step of few tokens cut its keys between blocks."""
     fn = _function("latent", "vipera_latent_attention", [ctypes.POINTER(_LatentParams), _c_int, _c_void])
     _check_struct("latent", "vipera_latent_params_size", _LatentParams)
     tokens = proj.shape[0]
@@ -1483,6 +1503,13 @@ def latent_attention(proj: torch.Tensor, *, q_off: int, g_off: int, kv_off: int,
     p.num_tokens, p.heads, p.d, p.rot, p.dv, p.rank = int(tokens), int(heads), int(head_dim), int(rot_dim), int(value_dim), int(rank)
     p.table_width, p.page_size = int(block_table.shape[1]), int(page_size)
     p.scale, p.eps = float(scale), float(eps)
+    p.part, p.split_keys, p.num_splits = None, 0, 1
+    if part is not None and max_keys > 0:
+        _, _, split_keys, splits = latent_plan(tokens, heads, int(max_keys), sm_count(proj.device))
+        if splits > 1:
+            if part.numel() < splits * tokens * heads * (rank + 2):
+                raise InvalidArgumentError("latent_attention: the scratch of the splits is too small")
+            p.part, p.split_keys, p.num_splits = _gpu(part, "part", torch.float32), int(split_keys), int(splits)
     _check(fn(ctypes.byref(p), dtype_code(k_pool.dtype), _stream()), "attention", kernels=4 if kv_off >= 0 else 3)
 
 

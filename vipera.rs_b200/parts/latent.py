@@ -14,7 +14,9 @@ expanded.  The pages hold the latents where other attention keeps keys (one "KV 
 values) and the rotated key part where it keeps values (``rot_dim`` values).  A layer built with
 ``own_cache = False`` has no down projection: it reads the pages another layer of the same latent
 geometry wrote in this step (the schedule hands it that layer's cache slot without write access).
-Scores, softmax, the sums over keys, the latent's norm and the rotation are 32-bit.
+Scores, softmax, the sums over keys, the latent's norm and the rotation are 32-bit.  In bfloat16
+the fold over the keys runs on the tensor cores, sixteen (token, head) rows of one request to a
+block, and a step of few tokens cuts its keys between blocks.
 """
 from __future__ import annotations
 
@@ -100,7 +102,9 @@ class LatentAttention(Mixer):
     def workspace_bytes(cls, params, tokens, element_bytes):
         heads, rank, r = params["num_heads"], params["kv_rank"], params["rot_dim"]
         width = heads * (params["head_dim"] + r + params["value_dim"]) + rank + r
-        return tokens * (width * 4 + heads * (2 * rank + r) * 4 + heads * params["value_dim"] * element_bytes)
+        # (the splits of a step of few tokens: at most some 600 blocks of 16 rows more than the step's own)
+        return (tokens * (width * 4 + heads * (2 * rank + r) * 4 + heads * params["value_dim"] * element_bytes)
+                + 16 * (rank + 2) * 4 * 1300)
 
     def forward(self, ctx, h, residual, cache, writes_cache):
         if writes_cache != self.own_cache:
@@ -112,11 +116,15 @@ class LatentAttention(Mixer):
         mixed_latent = ws.get("latent.mixed", (count, self.heads, self.rank), torch.float32)
         mixed = ws.get("latent.out", (count, self.heads * self.vdim), ctx.dtype)
         cos, sin = self.position.tables()
+        max_keys = max(int(ctx.max_kv_len), 1)
+        floats = ops.latent_part_floats(count, self.heads, self.rank, max_keys, ops.sm_count(h.device)) if ctx.dtype == torch.bfloat16 else 0
+        part = ws.get("latent.part", (floats,), torch.float32) if floats else None
         ops.latent_attention(proj, q_off=self.q_off, g_off=self.g_off, kv_off=self.kv_off, up_k=self.up_k, up_v=self.up_v,
                              norm_weight=self.latent_norm, eps=self.norm_eps, positions=ctx.positions,
                              token_entry=ctx.token_entry, block_table=ctx.block_tables[cache.group], cos=cos, sin=sin,
                              k_pool=cache.k, v_pool=cache.v, qa=qa, latent_out=mixed_latent, out=mixed, heads=self.heads,
-                             head_dim=self.dim, rot_dim=self.rot, value_dim=self.vdim, scale=self.scale)
+                             head_dim=self.dim, rot_dim=self.rot, value_dim=self.vdim, scale=self.scale, max_keys=max_keys,
+                             part=part)
         self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
 
 
