@@ -319,20 +319,28 @@ latent_fold_kernel(LatentFoldParams p) {
     const int num_tiles = end > begin ? (end - begin + kFoldKeys - 1) / kFoldKeys : 0;
     const int* table = p.block_table + static_cast<size_t>(entry) * p.table_width;
 
+    // A warp copies 8 keys of a tile: their page-table entries first (all lanes the same loads, in
+    // flight together), then each row's 16-byte pieces, a lane taking every 32nd.
     auto copy_tile = [&](int tile) {
       __nv_bfloat16* dst_tile = k_s + (tile & 1) * kFoldKeys * stride;
-      const int key0 = begin + tile * kFoldKeys;
-      for (int i = threadIdx.x; i < kFoldKeys * row_chunks; i += kFoldThreads) {
-        const int local = i / row_chunks, chunk = i % row_chunks;
-        const int key = key0 + local;
-        const bool valid = key < end;
-        const __nv_bfloat16* src = p.k_pool;
-        if (valid) {
-          const size_t slot = static_cast<size_t>(table[key / p.page_size]) * p.page_size + key % p.page_size;
-          src = chunk < rank_chunks ? p.k_pool + slot * p.rank + chunk * 8 : p.v_pool + slot * p.rot + (chunk - rank_chunks) * 8;
+      const int key0 = begin + tile * kFoldKeys + warp * 8;
+      size_t slots[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int key = min(key0 + i, end - 1);
+        slots[i] = static_cast<size_t>(table[key / p.page_size]) * p.page_size + key % p.page_size;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const bool valid = key0 + i < end;
+        const __nv_bfloat16* c_row = p.k_pool + slots[i] * p.rank;
+        const __nv_bfloat16* r_row = p.v_pool + slots[i] * p.rot;
+        __nv_bfloat16* dst = dst_tile + (warp * 8 + i) * stride;
+        for (int chunk = lane; chunk < row_chunks; chunk += 32) {
+          const bool latent = chunk < rank_chunks;
+          cp_async_16(smem_addr(dst + (latent ? chunk * 8 : rank_pad + (chunk - rank_chunks) * 8)),
+                      latent ? c_row + chunk * 8 : r_row + (chunk - rank_chunks) * 8, valid);
         }
-        const int column = chunk < rank_chunks ? chunk * 8 : rank_pad + (chunk - rank_chunks) * 8;
-        cp_async_16(smem_addr(dst_tile + local * stride + column), src, valid);
       }
       cp_async_commit();
     };
@@ -353,7 +361,7 @@ latent_fold_kernel(LatentFoldParams p) {
       const __nv_bfloat16* keys = k_s + (tile & 1) * kFoldKeys * stride;
       const int key0 = begin + tile * kFoldKeys;
       {
-        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c_odd[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // two chains of products
         const uint32_t k_addr = smem_addr(keys + (warp * 8 + (lane & 7)) * stride + (lane >> 3) * 8);
         const uint32_t q_addr = smem_addr(q_s + ((lane & 7) + ((lane >> 3) & 1) * 8) * stride + (lane >> 4) * 8);
         for (int k0 = 0; k0 < width_pad; k0 += 32) {
@@ -361,9 +369,12 @@ latent_fold_kernel(LatentFoldParams p) {
           ldmatrix_x4(b, k_addr + k0 * 2);
           ldmatrix_x4(a, q_addr + k0 * 2);
           mma_16816(c, a, b[0], b[1]);
-          ldmatrix_x4(a, q_addr + (k0 + 16) * 2);
-          mma_16816(c, a, b[2], b[3]);
+          uint32_t a_odd[4];
+          ldmatrix_x4(a_odd, q_addr + (k0 + 16) * 2);
+          mma_16816(c_odd, a_odd, b[2], b[3]);
         }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) c[e] += c_odd[e];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int row = g + (e >> 1) * 8, col = warp * 8 + pair + (e & 1);
@@ -489,10 +500,16 @@ __global__ void __launch_bounds__(128)
 latent_expand_kernel(const float* __restrict__ latent_out, const TW* __restrict__ up_v, const float* __restrict__ proj,
                      long long proj_width, int g_off, TO* __restrict__ out, int num_tokens, int heads, int dv,
                      int rank) {
-  extern __shared__ float l_tile[];   // [kTile][rank]
+  // A block: kTile tokens of one head, 32 values; its four warps share the rank between them and
+  // add their parts in the warps' order.
+  extern __shared__ float expand_shared[];
+  float* l_tile = expand_shared;                 // [kTile][rank]
+  float* partial = expand_shared + kTile * rank; // [4][kTile][32]
   pdl_launch_dependents();
   pdl_wait();
   const int t0 = blockIdx.x * kTile, h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int v = blockIdx.z * 32 + lane;
   const int count = min(kTile, num_tokens - t0);
   for (int i = threadIdx.x; i < kTile * rank; i += blockDim.x) {
     const int tt = i / rank, r = i % rank;
@@ -500,24 +517,31 @@ latent_expand_kernel(const float* __restrict__ latent_out, const TW* __restrict_
   }
   __syncthreads();
   const TW* w = up_v + static_cast<size_t>(h) * rank * dv;
-  for (int v = threadIdx.x; v < dv; v += blockDim.x) {
-    float acc[kTile];
+  const int share = (rank + 3) / 4;
+  const int r_end = min(rank, (warp + 1) * share);
+  float acc[kTile];
 #pragma unroll
-    for (int tt = 0; tt < kTile; ++tt) acc[tt] = 0.0f;
+  for (int tt = 0; tt < kTile; ++tt) acc[tt] = 0.0f;
+  if (v < dv) {
 #pragma unroll 8
-    for (int r = 0; r < rank; ++r) {
+    for (int r = warp * share; r < r_end; ++r) {
       const float x = to_float<TW>(w[static_cast<size_t>(r) * dv + v]);
 #pragma unroll
       for (int tt = 0; tt < kTile; ++tt) acc[tt] = fmaf(l_tile[tt * rank + r], x, acc[tt]);
     }
+  }
 #pragma unroll
-    for (int tt = 0; tt < kTile; ++tt) {
-      if (tt >= count) continue;
-      const size_t t = t0 + tt;
-      float y = acc[tt];
-      if (g_off >= 0) y *= 1.0f / (1.0f + expf(-proj[t * proj_width + g_off + h * dv + v]));
-      out[(t * heads + h) * dv + v] = from_float<TO>(y);
-    }
+  for (int tt = 0; tt < kTile; ++tt) partial[(warp * kTile + tt) * 32 + lane] = acc[tt];
+  __syncthreads();
+  for (int i = threadIdx.x; i < kTile * 32; i += blockDim.x) {
+    const int tt = i / 32, column = blockIdx.z * 32 + i % 32;
+    if (tt >= count || column >= dv) continue;
+    float y = partial[i];
+#pragma unroll
+    for (int part = 1; part < 4; ++part) y += partial[part * kTile * 32 + i];
+    const size_t t = t0 + tt;
+    if (g_off >= 0) y *= 1.0f / (1.0f + expf(-proj[t * proj_width + g_off + h * dv + column]));
+    out[(t * heads + h) * dv + column] = from_float<TO>(y);
   }
 }
 
@@ -636,8 +660,8 @@ static int launch_latent(const LatentParams& p, cudaStream_t s) {
                            static_cast<const T*>(p.k_pool), static_cast<const T*>(p.v_pool), p.token_entry, p.positions,
                            p.block_table, p.table_width, p.page_size, p.heads, p.rank, p.rot);
   if (status) return status;
-  const int threads = p.dv >= 128 ? 128 : (p.dv + 31) / 32 * 32;
-  return vipera_launch(latent_expand_kernel<T, T>, tiles, threads, kTile * p.rank * sizeof(float), s, p.latent_out,
+  const dim3 expand_grid(tiles.x, tiles.y, (p.dv + 31) / 32);
+  return vipera_launch(latent_expand_kernel<T, T>, expand_grid, 128, (kTile * p.rank + 4 * kTile * 32) * sizeof(float), s, p.latent_out,
                        static_cast<const T*>(p.up_v), p.proj, p.proj_width, p.g_off, static_cast<T*>(p.out),
                        p.num_tokens, p.heads, p.dv, p.rank);
 }

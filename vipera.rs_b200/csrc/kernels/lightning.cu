@@ -8,8 +8,9 @@
 // and the concatenated heads' o is divided by its root mean square over the whole row, multiplied by a
 // weight per value and by sigmoid(gate) (lightning_finish_kernel).
 //
-// A block owns 32 value columns of a head's state for one job; a lane a column, the warps the rows
-// in turn (rows w, w + 4, ...), each thread's share of S in registers.  The operands of kStage
+// A block owns 32 value columns of a head's state for one job; a lane a column, a warp a run of
+// neighbouring rows (so that a thread reads its rows' k and q four at a time from shared memory),
+// each thread's share of S in registers.  The operands of kStage
 // tokens (silu applied) are staged in shared memory; the four warps' partial outputs are added in
 // a fixed order.  Three kinds of job (own notation; a chunk is kChunk tokens of one entry, cut
 // where the entry's tokens start in the step):
@@ -70,7 +71,7 @@ __device__ __forceinline__ void find_chunk(const int* __restrict__ entry_starts,
 template <int RPT, int MODE>
 __global__ void __launch_bounds__(kRowWarps * 32)
 lightning_scan_kernel(LightningParams p) {
-  extern __shared__ float shared[];
+  extern __shared__ __align__(16) float shared[];
   float* q_s = shared;                       // [kStage][d]
   float* k_s = q_s + kStage * p.d;           // [kStage][d]
   float* v_s = k_s + kStage * p.d;           // [kStage][kColumns]
@@ -103,7 +104,7 @@ lightning_scan_kernel(LightningParams p) {
   const bool load = MODE == MODE_OUTPUTS || (MODE == MODE_WALK && !p.fresh[entry]);
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
-    const int row = warp + kRowWarps * i;
+    const int row = warp * RPT + i;
     s[i] = (load && live && row < p.d) ? own[static_cast<size_t>(row) * p.dv + column] : 0.0f;
   }
   for (int base = begin; base < end; base += kStage) {
@@ -120,15 +121,36 @@ lightning_scan_kernel(LightningParams p) {
       v_s[i] = c < p.dv ? silu(p.proj[static_cast<size_t>(base + tt) * p.proj_width + p.v_off + h * p.dv + c]) : 0.0f;
     }
     __syncthreads();
+    const bool whole_rows = (p.d & 3) == 0 && (warp + 1) * RPT <= p.d;   // this warp's rows all exist, in fours
     for (int tt = 0; tt < count; ++tt) {
       const float v = v_s[tt * kColumns + lane];
       float o = 0.0f;
+      if (RPT % 4 == 0 && whole_rows) {
+        const float4* k4 = reinterpret_cast<const float4*>(k_s + tt * p.d + warp * RPT);
+        const float4* q4 = reinterpret_cast<const float4*>(q_s + tt * p.d + warp * RPT);
 #pragma unroll
-      for (int i = 0; i < RPT; ++i) {
-        const int row = warp + kRowWarps * i;
-        if (row < p.d) {
-          s[i] = fmaf(lambda, s[i], k_s[tt * p.d + row] * v);
-          if (MODE != MODE_ENDS) o = fmaf(s[i], q_s[tt * p.d + row], o);
+        for (int i = 0; i < RPT / 4; ++i) {
+          const float4 kk = k4[i];
+          s[4 * i] = fmaf(lambda, s[4 * i], kk.x * v);
+          s[4 * i + 1] = fmaf(lambda, s[4 * i + 1], kk.y * v);
+          s[4 * i + 2] = fmaf(lambda, s[4 * i + 2], kk.z * v);
+          s[4 * i + 3] = fmaf(lambda, s[4 * i + 3], kk.w * v);
+          if (MODE != MODE_ENDS) {
+            const float4 qq = q4[i];
+            o = fmaf(s[4 * i], qq.x, o);
+            o = fmaf(s[4 * i + 1], qq.y, o);
+            o = fmaf(s[4 * i + 2], qq.z, o);
+            o = fmaf(s[4 * i + 3], qq.w, o);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+          const int row = warp * RPT + i;
+          if (row < p.d) {
+            s[i] = fmaf(lambda, s[i], k_s[tt * p.d + row] * v);
+            if (MODE != MODE_ENDS) o = fmaf(s[i], q_s[tt * p.d + row], o);
+          }
         }
       }
       if (MODE != MODE_ENDS) part[(tt * kRowWarps + warp) * kColumns + lane] = o;
@@ -148,7 +170,7 @@ lightning_scan_kernel(LightningParams p) {
   if (MODE != MODE_OUTPUTS && live) {
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
-      const int row = warp + kRowWarps * i;
+      const int row = warp * RPT + i;
       if (row < p.d) own[static_cast<size_t>(row) * p.dv + column] = s[i];
     }
   }
@@ -172,17 +194,25 @@ lightning_carry_kernel(LightningParams p) {
   float s = p.fresh[entry] ? 0.0f : *own;
   float whole = 1.0f;   // lambda^kChunk by repeated multiplication, the same way the scan applies it
   for (int i = 0; i < kChunk; ++i) whole *= lambda;
-  for (int begin = start; begin < stop; begin += kChunk, ++job) {
-    const int length = min(kChunk, stop - begin);
-    float* slot = p.chunk_state + static_cast<size_t>(job) * state_size + element;
-    const float ending = *slot;
-    *slot = s;
-    float power = whole;
-    if (length < kChunk) {
-      power = 1.0f;
-      for (int i = 0; i < length; ++i) power *= lambda;
+  // eight chunks at a time: their endings are asked for together, then walked in order
+  for (int begin = start; begin < stop; begin += 8 * kChunk, job += 8) {
+    float ending[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      ending[c] = begin + c * kChunk < stop ? p.chunk_state[static_cast<size_t>(job + c) * state_size + element] : 0.0f;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int first = begin + c * kChunk;
+      if (first >= stop) break;
+      const int length = min(kChunk, stop - first);
+      p.chunk_state[static_cast<size_t>(job + c) * state_size + element] = s;
+      float power = whole;
+      if (length < kChunk) {
+        power = 1.0f;
+        for (int i = 0; i < length; ++i) power *= lambda;
+      }
+      s = fmaf(power, s, ending[c]);
     }
-    s = fmaf(power, s, ending);
   }
   *own = s;
 }
