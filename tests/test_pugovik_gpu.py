@@ -448,6 +448,7 @@ FOLDS = {
     "decode": ((12, 32, 64, 32, 512), [(700, 1), (63, 1), (0, 1), (1029, 1), (64, 1)]),
     "small": ((3, 16, 8, 8, 40), [(0, 70), (33, 2), (200, 1), (0, 1), (5, 11)]),
     "many_heads": ((20, 8, 24, 16, 136), [(90, 3), (300, 1), (0, 9)]),
+    "long_prompts": ((3, 16, 8, 8, 40), [(0, 903), (37, 650)]),   # enough rows for blocks of two groups of sixteen
 }
 
 

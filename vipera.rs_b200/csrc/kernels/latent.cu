@@ -253,7 +253,7 @@ struct LatentFoldParams {
 
 __host__ __device__ __forceinline__ int round_up(int v, int to) { return (v + to - 1) / to * to; }
 
-template <int NR>
+template <int NR, int MT>
 __global__ void __launch_bounds__(kFoldThreads)
 latent_fold_kernel(LatentFoldParams p) {
   extern __shared__ __align__(16) unsigned char fold_shared[];
@@ -261,19 +261,20 @@ latent_fold_kernel(LatentFoldParams p) {
   const int width_pad = round_up(rank_pad + round_up(p.rot, 16), 32);
   const int stride = width_pad + 8;   // bf16 per row: rows 16 bytes apart modulo 128, so ldmatrix meets no bank twice
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(fold_shared);
-  __nv_bfloat16* k_s = q_s + kFoldRows * stride;                       // two tiles of kFoldKeys rows
+  constexpr int kRows = kFoldRows * MT;   // MT groups of sixteen rows share every tile of keys
+  __nv_bfloat16* k_s = q_s + kRows * stride;                       // two tiles of kFoldKeys rows
   float* s_s = reinterpret_cast<float*>(k_s + 2 * kFoldKeys * stride);
-  __nv_bfloat16* p_s = reinterpret_cast<__nv_bfloat16*>(s_s + kFoldRows * kScoreStride);
-  float* m_s = reinterpret_cast<float*>(p_s + kFoldRows * kWeightStride);
-  float* l_s = m_s + kFoldRows;
-  float* alpha_s = l_s + kFoldRows;
-  int* limit_s = reinterpret_cast<int*>(alpha_s + kFoldRows);
-  int* row_s = limit_s + kFoldRows;
+  __nv_bfloat16* p_s = reinterpret_cast<__nv_bfloat16*>(s_s + kRows * kScoreStride);
+  float* m_s = reinterpret_cast<float*>(p_s + kRows * kWeightStride);
+  float* l_s = m_s + kRows;
+  float* alpha_s = l_s + kRows;
+  int* limit_s = reinterpret_cast<int*>(alpha_s + kRows);
+  int* row_s = limit_s + kRows;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   {
     // everything the copies never write (the columns that pad rank and rot) must read as zero
     uint4* all = reinterpret_cast<uint4*>(fold_shared);
-    const int vectors = (kFoldRows + 2 * kFoldKeys) * stride * 2 / 16;
+    const int vectors = (kRows + 2 * kFoldKeys) * stride * 2 / 16;
     for (int i = threadIdx.x; i < vectors; i += kFoldThreads) all[i] = make_uint4(0u, 0u, 0u, 0u);
   }
   pdl_launch_dependents();
@@ -299,7 +300,7 @@ latent_fold_kernel(LatentFoldParams p) {
         last_key = max(last_key, p.positions[t0 + tq]);
       }
     __syncthreads();   // the pass before is done with the rows' tables
-    if (threadIdx.x < kFoldRows) {
+    if (threadIdx.x < kRows) {
       const int r = threadIdx.x, tq = r / p.head_group, head = head0 + r % p.head_group;
       const bool valid = tq < p.tokens_per_tile && ((taken >> tq) & 1u) && head < p.heads;
       limit_s[r] = valid ? p.positions[t0 + tq] : -1;
@@ -309,7 +310,7 @@ latent_fold_kernel(LatentFoldParams p) {
     }
     done |= taken;
     __syncthreads();
-    for (int i = threadIdx.x; i < kFoldRows * width; i += kFoldThreads) {
+    for (int i = threadIdx.x; i < kRows * width; i += kFoldThreads) {
       const int r = i / width, c = i % width;
       const float v = row_s[r] >= 0 ? p.qa[static_cast<size_t>(row_s[r]) * width + c] : 0.0f;
       q_s[r * stride + (c < p.rank ? c : rank_pad + c - p.rank)] = __float2bfloat16(v);
@@ -346,11 +347,13 @@ latent_fold_kernel(LatentFoldParams p) {
     };
 
     constexpr int kPairs = NR / 8 / 16;   // pairs of 8-column tiles a warp accumulates
-    float acc[2 * kPairs][4];
+    float acc[MT][2 * kPairs][4];
 #pragma unroll
-    for (int j = 0; j < 2 * kPairs; ++j)
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) acc[j][e] = 0.0f;
+      for (int j = 0; j < 2 * kPairs; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[mt][j][e] = 0.0f;
     const int column0 = warp * (NR / 8);
     const int g = lane >> 2, pair = (lane & 3) * 2;
     if (num_tiles > 0) copy_tile(0);
@@ -361,31 +364,39 @@ latent_fold_kernel(LatentFoldParams p) {
       const __nv_bfloat16* keys = k_s + (tile & 1) * kFoldKeys * stride;
       const int key0 = begin + tile * kFoldKeys;
       {
-        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c_odd[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // two chains of products
+        float c[MT][4], c_odd[MT][4];   // two chains of products per group of rows
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) c[mt][e] = c_odd[mt][e] = 0.0f;
         const uint32_t k_addr = smem_addr(keys + (warp * 8 + (lane & 7)) * stride + (lane >> 3) * 8);
         const uint32_t q_addr = smem_addr(q_s + ((lane & 7) + ((lane >> 3) & 1) * 8) * stride + (lane >> 4) * 8);
+#pragma unroll 2
         for (int k0 = 0; k0 < width_pad; k0 += 32) {
-          uint32_t b[4], a[4];
+          uint32_t b[4];
           ldmatrix_x4(b, k_addr + k0 * 2);
-          ldmatrix_x4(a, q_addr + k0 * 2);
-          mma_16816(c, a, b[0], b[1]);
-          uint32_t a_odd[4];
-          ldmatrix_x4(a_odd, q_addr + (k0 + 16) * 2);
-          mma_16816(c_odd, a_odd, b[2], b[3]);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            uint32_t a[4], a_odd[4];
+            ldmatrix_x4(a, q_addr + (mt * kFoldRows * stride + k0) * 2);
+            ldmatrix_x4(a_odd, q_addr + (mt * kFoldRows * stride + k0 + 16) * 2);
+            mma_16816(c[mt], a, b[0], b[1]);
+            mma_16816(c_odd[mt], a_odd, b[2], b[3]);
+          }
         }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) c[e] += c_odd[e];
+        for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int row = g + (e >> 1) * 8, col = warp * 8 + pair + (e & 1);
-          const int key = key0 + col;
-          s_s[row * kScoreStride + col] = (key <= limit_s[row] && key < end) ? c[e] : -INFINITY;
-        }
+          for (int e = 0; e < 4; ++e) {
+            const int row = mt * kFoldRows + g + (e >> 1) * 8, col = warp * 8 + pair + (e & 1);
+            const int key = key0 + col;
+            s_s[row * kScoreStride + col] = (key <= limit_s[row] && key < end) ? c[mt][e] + c_odd[mt][e] : -INFINITY;
+          }
       }
       __syncthreads();
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int row = warp * 2 + i;
+      for (int i = 0; i < 2 * MT; ++i) {
+        const int row = warp * 2 * MT + i;
         const float v0 = s_s[row * kScoreStride + lane], v1 = s_s[row * kScoreStride + lane + 32];
         const float before = m_s[row];
         const float top = fmaxf(before, warp_max(fmaxf(v0, v1)));
@@ -406,25 +417,32 @@ latent_fold_kernel(LatentFoldParams p) {
       }
       __syncthreads();
       {
-        const float alpha0 = alpha_s[g], alpha1 = alpha_s[g + 8];
 #pragma unroll
-        for (int j = 0; j < 2 * kPairs; ++j) {
-          acc[j][0] *= alpha0, acc[j][1] *= alpha0;
-          acc[j][2] *= alpha1, acc[j][3] *= alpha1;
+        for (int mt = 0; mt < MT; ++mt) {
+          const float alpha0 = alpha_s[mt * kFoldRows + g], alpha1 = alpha_s[mt * kFoldRows + g + 8];
+#pragma unroll
+          for (int j = 0; j < 2 * kPairs; ++j) {
+            acc[mt][j][0] *= alpha0, acc[mt][j][1] *= alpha0;
+            acc[mt][j][2] *= alpha1, acc[mt][j][3] *= alpha1;
+          }
         }
         const uint32_t p_addr = smem_addr(p_s + ((lane & 7) + ((lane >> 3) & 1) * 8) * kWeightStride + (lane >> 4) * 8);
         const uint32_t c_addr = smem_addr(keys + ((lane & 7) + ((lane >> 3) & 1) * 8) * stride + column0 + (lane >> 4) * 8);
 #pragma unroll
         for (int kk = 0; kk < kFoldKeys / 16; ++kk) {
-          uint32_t a[4];
-          ldmatrix_x4(a, p_addr + kk * 16 * 2);
+          uint32_t a[MT][4];
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(a[mt], p_addr + (mt * kFoldRows * kWeightStride + kk * 16) * 2);
 #pragma unroll
           for (int j = 0; j < kPairs; ++j) {
             if (column0 + 16 * j < rank_pad) {
               uint32_t b[4];
               ldmatrix_x4_trans(b, c_addr + (kk * 16 * stride + 16 * j) * 2);
-              mma_16816(acc[2 * j], a, b[0], b[1]);
-              mma_16816(acc[2 * j + 1], a, b[2], b[3]);
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt) {
+                mma_16816(acc[mt][2 * j], a[mt], b[0], b[1]);
+                mma_16816(acc[mt][2 * j + 1], a[mt], b[2], b[3]);
+              }
             }
           }
         }
@@ -432,8 +450,9 @@ latent_fold_kernel(LatentFoldParams p) {
     }
     __syncthreads();   // the last sums are written
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int row = g + half * 8;
+    for (int part_row = 0; part_row < 2 * MT; ++part_row) {
+      const int mt = part_row >> 1, half = part_row & 1;
+      const int row = mt * kFoldRows + g + half * 8;
       const int out_row = row_s[row];
       if (out_row < 0) continue;
       const float total = l_s[row];
@@ -442,16 +461,16 @@ latent_fold_kernel(LatentFoldParams p) {
 #pragma unroll
         for (int j = 0; j < 2 * kPairs; ++j) {
           const int col = column0 + 8 * j + pair;
-          if (col < p.rank) p.out[static_cast<size_t>(out_row) * p.rank + col] = acc[j][2 * half] * inverse;
-          if (col + 1 < p.rank) p.out[static_cast<size_t>(out_row) * p.rank + col + 1] = acc[j][2 * half + 1] * inverse;
+          if (col < p.rank) p.out[static_cast<size_t>(out_row) * p.rank + col] = acc[mt][j][2 * half] * inverse;
+          if (col + 1 < p.rank) p.out[static_cast<size_t>(out_row) * p.rank + col + 1] = acc[mt][j][2 * half + 1] * inverse;
         }
       } else {
         float* part = p.part + (static_cast<size_t>(split) * total_rows + out_row) * (p.rank + 2);
 #pragma unroll
         for (int j = 0; j < 2 * kPairs; ++j) {
           const int col = column0 + 8 * j + pair;
-          if (col < p.rank) part[col] = acc[j][2 * half];
-          if (col + 1 < p.rank) part[col + 1] = acc[j][2 * half + 1];
+          if (col < p.rank) part[col] = acc[mt][j][2 * half];
+          if (col + 1 < p.rank) part[col + 1] = acc[mt][j][2 * half + 1];
         }
         if (warp == 0 && pair == 0) {
           part[p.rank] = m_s[row];
@@ -571,9 +590,17 @@ struct LatentParams {
 // How the tensor-core fold cuts a step: {tokens per tile, heads per tile, keys per split, splits}.
 // Few blocks (decode) are cut along the keys, in whole tiles of 64, until the device has some
 // four blocks per SM.
-static void latent_plan(int tokens, int heads, int max_keys, int sms, int* plan) {
+// Groups of sixteen rows a block takes: two where single groups would still fill the device twice.
+static int fold_groups(int tokens, int heads, int sms) {
   const int head_group = heads < kFoldRows ? heads : kFoldRows;
   const int per_tile = kFoldRows / head_group;
+  const long base = static_cast<long>((tokens + per_tile - 1) / per_tile) * ((heads + head_group - 1) / head_group);
+  return base >= 2L * sms && heads <= kFoldRows ? 2 : 1;
+}
+
+static void latent_plan(int tokens, int heads, int max_keys, int sms, int* plan) {
+  const int head_group = heads < kFoldRows ? heads : kFoldRows;
+  const int per_tile = kFoldRows * fold_groups(tokens, heads, sms) / head_group;
   const long base = static_cast<long>((tokens + per_tile - 1) / per_tile) * ((heads + head_group - 1) / head_group);
   int bound = kFoldKeys;
   while (bound < max_keys) bound *= 2;
@@ -595,15 +622,15 @@ VIPERA_API int vipera_latent_plan(int tokens, int heads, int max_keys, int sms, 
   return VIPERA_OK;
 }
 
-template <int NR>
+template <int NR, int MT>
 static int launch_fold(const LatentFoldParams& f, dim3 grid, size_t shared, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(latent_fold_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024) != cudaSuccess)
+    if (cudaFuncSetAttribute(latent_fold_kernel<NR, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024) != cudaSuccess)
       return VIPERA_BAD_ARGUMENT;
     configured = true;
   }
-  return vipera_launch(latent_fold_kernel<NR>, grid, kFoldThreads, shared, s, f);
+  return vipera_launch(latent_fold_kernel<NR, MT>, grid, kFoldThreads, shared, s, f);
 }
 
 static int launch_fold_any(const LatentParams& p, cudaStream_t s) {
@@ -618,18 +645,28 @@ static int launch_fold_any(const LatentParams& p, cudaStream_t s) {
   f.part = p.part;
   f.num_tokens = p.num_tokens, f.heads = p.heads, f.rank = p.rank, f.rot = p.rot;
   f.table_width = p.table_width, f.page_size = p.page_size;
+  int device = 0, sms = 0;
+  cudaGetDevice(&device);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  const int groups = fold_groups(p.num_tokens, p.heads, sms > 0 ? sms : 148);
   f.head_group = p.heads < kFoldRows ? p.heads : kFoldRows;
-  f.tokens_per_tile = kFoldRows / f.head_group;
+  f.tokens_per_tile = kFoldRows * groups / f.head_group;
   f.num_splits = p.num_splits > 1 && p.part ? p.num_splits : 1;
   f.split_keys = f.num_splits > 1 ? p.split_keys : 0x3fffffff;
   const int rank_pad = round_up(p.rank, 16);
   const int stride = round_up(rank_pad + round_up(p.rot, 16), 32) + 8;
-  const size_t shared = static_cast<size_t>(kFoldRows + 2 * kFoldKeys) * stride * 2 + kFoldRows * kScoreStride * 4 +
-                        kFoldRows * kWeightStride * 2 + kFoldRows * 5 * 4;
+  const int rows = kFoldRows * groups;
+  const size_t shared = static_cast<size_t>(rows + 2 * kFoldKeys) * stride * 2 + rows * kScoreStride * 4 +
+                        rows * kWeightStride * 2 + rows * 5 * 4;
   const dim3 grid((p.num_tokens + f.tokens_per_tile - 1) / f.tokens_per_tile, (p.heads + f.head_group - 1) / f.head_group,
                   f.num_splits);
-  int status = rank_pad <= 128 ? launch_fold<128>(f, grid, shared, s)
-             : rank_pad <= 256 ? launch_fold<256>(f, grid, shared, s) : launch_fold<512>(f, grid, shared, s);
+  int status;
+  if (groups == 2)
+    status = rank_pad <= 128 ? launch_fold<128, 2>(f, grid, shared, s)
+           : rank_pad <= 256 ? launch_fold<256, 2>(f, grid, shared, s) : launch_fold<512, 2>(f, grid, shared, s);
+  else
+    status = rank_pad <= 128 ? launch_fold<128, 1>(f, grid, shared, s)
+           : rank_pad <= 256 ? launch_fold<256, 1>(f, grid, shared, s) : launch_fold<512, 1>(f, grid, shared, s);
   if (status || f.num_splits == 1) return status;
   return vipera_launch(latent_combine_kernel, p.num_tokens * p.heads, 128, 0, s, f);
 }
