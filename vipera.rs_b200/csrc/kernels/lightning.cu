@@ -46,6 +46,7 @@ struct LightningParams {
   float* chunk_state;       // [jobs, heads * d * dv] (chunked form only)
   int heads, d, dv, num_entries, num_tokens, num_jobs;
   float eps;
+  int activated;            // 1: q, k and v in proj are past their silu already (the chunked form's first kernel)
 };
 
 __device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }
@@ -66,6 +67,25 @@ __device__ __forceinline__ void find_chunk(const int* __restrict__ entry_starts,
     }
     base += chunks;
   }
+}
+
+// The chunked form reads every token's q and k in each block of its head's columns, twice: the silu
+// is applied once, in place (the gate's columns stay as they are).
+__global__ void __launch_bounds__(256)
+lightning_activate_kernel(LightningParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_token = p.heads * (2 * p.d + p.dv);
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<long long>(p.num_tokens) * per_token) return;
+  const long long t = i / per_token;
+  int c = static_cast<int>(i % per_token);
+  int column;
+  if (c < p.heads * p.d) column = p.q_off + c;
+  else if ((c -= p.heads * p.d) < p.heads * p.d) column = p.k_off + c;
+  else column = p.v_off + c - p.heads * p.d;
+  float* at = const_cast<float*>(p.proj) + t * p.proj_width + column;
+  *at = silu(*at);
 }
 
 template <int RPT, int MODE>
@@ -113,12 +133,14 @@ lightning_scan_kernel(LightningParams p) {
     for (int i = threadIdx.x; i < count * p.d; i += blockDim.x) {
       const int tt = i / p.d, e = i % p.d;
       const float* row = p.proj + static_cast<size_t>(base + tt) * p.proj_width;
-      if (MODE != MODE_ENDS) q_s[tt * p.d + e] = silu(row[p.q_off + h * p.d + e]);
-      k_s[tt * p.d + e] = silu(row[p.k_off + h * p.d + e]);
+      const float q_raw = MODE != MODE_ENDS ? row[p.q_off + h * p.d + e] : 0.0f, k_raw = row[p.k_off + h * p.d + e];
+      if (MODE != MODE_ENDS) q_s[tt * p.d + e] = (MODE != MODE_WALK && p.activated) ? q_raw : silu(q_raw);
+      k_s[tt * p.d + e] = (MODE != MODE_WALK && p.activated) ? k_raw : silu(k_raw);
     }
     for (int i = threadIdx.x; i < count * kColumns; i += blockDim.x) {
       const int tt = i / kColumns, c = blockIdx.x * kColumns + i % kColumns;
-      v_s[i] = c < p.dv ? silu(p.proj[static_cast<size_t>(base + tt) * p.proj_width + p.v_off + h * p.dv + c]) : 0.0f;
+      const float v_raw = c < p.dv ? p.proj[static_cast<size_t>(base + tt) * p.proj_width + p.v_off + h * p.dv + c] : 0.0f;
+      v_s[i] = (MODE != MODE_WALK && p.activated) ? v_raw : silu(v_raw);
     }
     __syncthreads();
     const bool whole_rows = (p.d & 3) == 0 && (warp + 1) * RPT <= p.d;   // this warp's rows all exist, in fours
@@ -237,12 +259,18 @@ lightning_finish_kernel(LightningParams p) {
 }
 
 template <int RPT>
-static int launch_scans(const LightningParams& p, bool chunked, cudaStream_t s) {
+static int launch_scans(const LightningParams& params, bool chunked, cudaStream_t s) {
+  LightningParams p = params;
+  p.activated = 0;
   const size_t shared = (static_cast<size_t>(2 * kStage) * p.d + kStage * kColumns + kStage * kRowWarps * kColumns) * sizeof(float);
   const int tiles = (p.dv + kColumns - 1) / kColumns;
   if (!chunked)
     return vipera_launch(lightning_scan_kernel<RPT, MODE_WALK>, dim3(tiles, p.heads, p.num_entries), kRowWarps * 32, shared, s, p);
-  int status = vipera_launch(lightning_scan_kernel<RPT, MODE_ENDS>, dim3(tiles, p.heads, p.num_jobs), kRowWarps * 32, shared, s, p);
+  p.activated = 1;
+  const long long values = static_cast<long long>(p.num_tokens) * p.heads * (2 * p.d + p.dv);
+  int status = vipera_launch(lightning_activate_kernel, static_cast<unsigned>((values + 255) / 256), 256, 0, s, p);
+  if (status) return status;
+  status = vipera_launch(lightning_scan_kernel<RPT, MODE_ENDS>, dim3(tiles, p.heads, p.num_jobs), kRowWarps * 32, shared, s, p);
   if (status) return status;
   const size_t state_size = static_cast<size_t>(p.heads) * p.d * p.dv;
   status = vipera_launch(lightning_carry_kernel, dim3(static_cast<unsigned>((state_size + 255) / 256), p.num_entries), 256, 0, s, p);

@@ -1523,7 +1523,7 @@ class _LightningParams(ctypes.Structure):
         ("decay", _c_void), ("state", _c_void), ("entry_starts", _c_void), ("state_slots", _c_void), ("fresh", _c_void),
         ("raw", _c_void), ("norm_weight", _c_void), ("out", _c_void), ("chunk_state", _c_void),
         ("heads", _c_int), ("d", _c_int), ("dv", _c_int), ("num_entries", _c_int), ("num_tokens", _c_int),
-        ("num_jobs", _c_int), ("eps", _c_float),
+        ("num_jobs", _c_int), ("eps", _c_float), ("activated", _c_int),
     ]
 
 
@@ -1565,7 +1565,7 @@ def lightning(proj: torch.Tensor, *, offsets, heads: int, dim: int, vdim: int, d
             raise InvalidArgumentError("lightning: the chunk scratch has the wrong shape")
         p.num_jobs = jobs
         p.chunk_state = _gpu(chunk_state, "chunk states", torch.float32)
-    _check(fn(ctypes.byref(p), dtype_code(out.dtype), _stream()), "lightning", kernels=4 if chunk_state is not None else 2)
+    _check(fn(ctypes.byref(p), dtype_code(out.dtype), _stream()), "lightning", kernels=5 if chunk_state is not None else 2)
 
 
 # ----------------------------------------------------------------------------------------
