@@ -452,9 +452,10 @@ FOLDS = {
 }
 
 
+@pytest.mark.parametrize("head_major", [False, True])
 @pytest.mark.parametrize("cut", [False, True])
 @pytest.mark.parametrize("name", sorted(FOLDS))
-def test_the_fold_over_latents_alone(name, cut):
+def test_the_fold_over_latents_alone(name, cut, head_major):
     """The bfloat16 attention over cached latents on its own (the form on the tensor cores, with and
     without its keys cut between blocks): requests of unequal history in one step, tiles of rows
     that span requests, pages in a shuffled order, against a plain computation in 64-bit."""
@@ -507,12 +508,27 @@ def test_the_fold_over_latents_alone(name, cut):
     floats = ops.latent_part_floats(tokens, heads, rank, max_keys, ops.sm_count(torch.device(device)))
     assert floats > 0
     part = torch.full((floats,), float("nan"), dtype=torch.float32, device=device) if cut else None
+    buffers = None
+    if head_major:   # the products with the up matrices as grouped tensor-core products, a head a group
+        padded = -(-tokens // 128) * 128
+
+        def scratch(rows, columns, kind):
+            return torch.full((rows, columns), float("nan") if kind != torch.int32 else -1, dtype=kind, device=device)
+
+        buffers = {"padded": padded,
+                   "up_k_t": up_k.view(heads, d, rank).transpose(1, 2).contiguous().to(device),
+                   "up_v_rows": up_v.transpose(1, 2).contiguous().to(device),
+                   "a_heads": scratch(heads * padded, d, torch.bfloat16), "qa_heads": scratch(heads * padded, rank, torch.float32),
+                   "q_rot": scratch(tokens, heads * rot, torch.float32), "l_heads": scratch(heads * padded, rank, torch.bfloat16),
+                   "o_heads": scratch(heads * padded, dv, torch.float32),
+                   "tile_group": scratch(1, heads * padded // 128, torch.int32).view(-1)}
     ops.latent_attention(proj.to(device), q_off=0, g_off=q_width, kv_off=-1, up_k=up_k.to(device), up_v=up_v.to(device),
                          norm_weight=None, eps=1e-6, positions=torch.tensor(position, dtype=torch.int32, device=device),
                          token_entry=torch.tensor(entry, dtype=torch.int32, device=device), block_table=table.to(device),
                          cos=cos.float().to(device), sin=sin.float().to(device), k_pool=k_pool.to(device),
                          v_pool=v_pool.to(device), qa=qa, latent_out=mixed, out=out, heads=heads, head_dim=d, rot_dim=rot,
-                         value_dim=dv, scale=scale, max_keys=max_keys, part=part)
+                         value_dim=dv, scale=scale, max_keys=max_keys, part=part, head_major=buffers)
+    ops.check_kernel_status(torch.device(device))
     got = out.cpu().double()
     assert torch.isfinite(got).all()
     assert float((got - want).abs().max()) <= 2e-2 * float(want.abs().max())

@@ -249,6 +249,15 @@ struct LatentFoldParams {
   float* part;                     // splits: [num_splits][tokens * heads][rank + 2]: columns, then m and sum
   int num_tokens, heads, rank, rot, table_width, page_size;
   int head_group, tokens_per_tile, split_keys, num_splits;
+  // Head-major form (the products on both sides of the fold run as grouped tensor-core products, a
+  // head a group): the unrotated part of qa comes unscaled from qa_heads [heads, padded_tokens, rank]
+  // and the rotated, scaled part from q_rot [tokens, heads, rot]; the folded latents leave as
+  // bfloat16 rows of l_heads [heads, padded_tokens, rank].  Null: qa and out as above.
+  const float* qa_heads;
+  const float* q_rot;
+  __nv_bfloat16* l_heads;
+  int padded_tokens;
+  float scale;
 };
 
 __host__ __device__ __forceinline__ int round_up(int v, int to) { return (v + to - 1) / to * to; }
@@ -279,7 +288,7 @@ latent_fold_kernel(LatentFoldParams p) {
   }
   pdl_launch_dependents();
   pdl_wait();
-  const int t0 = blockIdx.x * p.tokens_per_tile;
+  const int t0 = (gridDim.x - 1 - blockIdx.x) * p.tokens_per_tile;   // the longest histories of a prompt first
   const int head0 = blockIdx.y * p.head_group;
   const int split = blockIdx.z;
   const int width = p.rank + p.rot;
@@ -312,7 +321,17 @@ latent_fold_kernel(LatentFoldParams p) {
     __syncthreads();
     for (int i = threadIdx.x; i < kRows * width; i += kFoldThreads) {
       const int r = i / width, c = i % width;
-      const float v = row_s[r] >= 0 ? p.qa[static_cast<size_t>(row_s[r]) * width + c] : 0.0f;
+      float v = 0.0f;
+      if (row_s[r] >= 0) {
+        if (p.qa_heads == nullptr) {
+          v = p.qa[static_cast<size_t>(row_s[r]) * width + c];
+        } else if (c < p.rank) {
+          const int token = row_s[r] / p.heads, head = row_s[r] % p.heads;
+          v = p.scale * p.qa_heads[(static_cast<size_t>(head) * p.padded_tokens + token) * p.rank + c];
+        } else {
+          v = p.q_rot[static_cast<size_t>(row_s[r]) * p.rot + c - p.rank];
+        }
+      }
       q_s[r * stride + (c < p.rank ? c : rank_pad + c - p.rank)] = __float2bfloat16(v);
     }
     const int begin = split * p.split_keys;
@@ -456,7 +475,16 @@ latent_fold_kernel(LatentFoldParams p) {
       const int out_row = row_s[row];
       if (out_row < 0) continue;
       const float total = l_s[row];
-      if (p.num_splits == 1) {
+      if (p.num_splits == 1 && p.l_heads != nullptr) {
+        const float inverse = 1.0f / total;
+        __nv_bfloat16* l_row = p.l_heads + (static_cast<size_t>(out_row % p.heads) * p.padded_tokens + out_row / p.heads) * p.rank;
+#pragma unroll
+        for (int j = 0; j < 2 * kPairs; ++j) {
+          const int col = column0 + 8 * j + pair;   // (even, and the rank is a multiple of 8)
+          if (col < p.rank)
+            *reinterpret_cast<uint32_t*>(l_row + col) = pack_bf16(acc[mt][j][2 * half] * inverse, acc[mt][j][2 * half + 1] * inverse);
+        }
+      } else if (p.num_splits == 1) {
         const float inverse = 1.0f / total;
 #pragma unroll
         for (int j = 0; j < 2 * kPairs; ++j) {
@@ -505,8 +533,60 @@ latent_combine_kernel(LatentFoldParams p) {
       const float* part = p.part + (s * rows + row) * each;
       if (part[p.rank + 1] > 0.0f) sum += part[c] * expf(part[p.rank] - top);
     }
-    p.out[static_cast<size_t>(row) * p.rank + c] = sum * inverse;
+    if (p.l_heads != nullptr)
+      p.l_heads[(static_cast<size_t>(row % p.heads) * p.padded_tokens + row / p.heads) * p.rank + c] = __float2bfloat16(sum * inverse);
+    else
+      p.out[static_cast<size_t>(row) * p.rank + c] = sum * inverse;
   }
+}
+
+// ---------------------------------------------------------------------------------------
+// Head-major form, in front of the fold: a block per token puts each head's unrotated q values
+// (bfloat16) at row [head, token] of a_heads [heads, padded_tokens, d], the operand of the grouped
+// product with U_h^T, and the rotated, scaled rest at q_rot [token, head, rot].  The first block
+// also fills the table that gives every tile of 128 rows its head.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+latent_prep_kernel(const float* __restrict__ proj, long long proj_width, int q_off, const int* __restrict__ positions,
+                   const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+                   __nv_bfloat16* __restrict__ a_heads, float* __restrict__ q_rot, int* __restrict__ tile_group,
+                   int heads, int d, int rot, int padded_tokens, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (t == 0)
+    for (int i = threadIdx.x; i < heads * (padded_tokens / 128); i += blockDim.x) tile_group[i] = i / (padded_tokens / 128);
+  const float* row = proj + static_cast<size_t>(t) * proj_width + q_off;
+  for (int i = threadIdx.x; i < heads * d; i += blockDim.x) {
+    const int h = i / d, e = i % d;
+    a_heads[(static_cast<size_t>(h) * padded_tokens + t) * d + e] = __float2bfloat16(row[h * (d + rot) + e]);
+  }
+  const int position = positions[t];
+  const float* cs = cos_table + static_cast<size_t>(position) * (rot / 2);
+  const float* sn = sin_table + static_cast<size_t>(position) * (rot / 2);
+  for (int i = threadIdx.x; i < heads * (rot / 2); i += blockDim.x) {
+    const int h = i / (rot / 2), pair = i % (rot / 2);
+    const float a = row[h * (d + rot) + d + 2 * pair], b = row[h * (d + rot) + d + 2 * pair + 1];
+    float* dst = q_rot + (static_cast<size_t>(t) * heads + h) * rot;
+    dst[2 * pair] = (a * cs[pair] - b * sn[pair]) * scale;
+    dst[2 * pair + 1] = (b * cs[pair] + a * sn[pair]) * scale;
+  }
+}
+
+// Head-major form, behind the second product: out[t, h * dv + v] = o_heads[h, t, v] * sigmoid(gate).
+template <typename TO>
+__global__ void __launch_bounds__(256)
+latent_gate_kernel(const float* __restrict__ o_heads, const float* __restrict__ proj, long long proj_width, int g_off,
+                   TO* __restrict__ out, int num_tokens, int heads, int dv, int padded_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<long long>(num_tokens) * heads * dv) return;
+  const long long t = i / (heads * dv);
+  const int c = static_cast<int>(i % (heads * dv)), h = c / dv, v = c % dv;
+  float y = o_heads[(static_cast<size_t>(h) * padded_tokens + t) * dv + v];
+  if (g_off >= 0) y *= 1.0f / (1.0f + expf(-proj[t * proj_width + g_off + c]));
+  out[i] = from_float<TO>(y);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -585,6 +665,17 @@ struct LatentParams {
   float scale, eps;
   float* part;             // scratch of the tensor-core fold's splits: [num_splits][tokens * heads][rank + 2], or null
   int split_keys, num_splits;   // as vipera_latent_plan gives them (1 split: the whole history in one block)
+  // Head-major form (bfloat16): the caller runs the grouped products between the stages.
+  //   stage 1: cache write, a_heads, q_rot, tile_group;  [qa_heads = a_heads x U_h^T]
+  //   stage 2: the fold, leaving l_heads;                [o_heads = l_heads x V_h^T]
+  //   stage 3: the gate and the output.    stage 0: everything in one call, without these buffers.
+  int stage, padded_tokens;
+  void* a_heads;           // [heads, padded_tokens, d]
+  float* qa_heads;         // [heads, padded_tokens, rank]
+  float* q_rot;            // [tokens, heads, rot]
+  void* l_heads;           // [heads, padded_tokens, rank]
+  float* o_heads;          // [heads, padded_tokens, dv]
+  int* tile_group;         // [heads * padded_tokens / 128]
 };
 
 // How the tensor-core fold cuts a step: {tokens per tile, heads per tile, keys per split, splits}.
@@ -645,6 +736,10 @@ static int launch_fold_any(const LatentParams& p, cudaStream_t s) {
   f.part = p.part;
   f.num_tokens = p.num_tokens, f.heads = p.heads, f.rank = p.rank, f.rot = p.rot;
   f.table_width = p.table_width, f.page_size = p.page_size;
+  if (p.stage == 2) {
+    f.qa_heads = p.qa_heads, f.q_rot = p.q_rot, f.l_heads = static_cast<__nv_bfloat16*>(p.l_heads);
+    f.padded_tokens = p.padded_tokens, f.scale = p.scale;
+  }
   int device = 0, sms = 0;
   cudaGetDevice(&device);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
@@ -674,6 +769,12 @@ static int launch_fold_any(const LatentParams& p, cudaStream_t s) {
 template <typename T>
 static int launch_latent(const LatentParams& p, cudaStream_t s) {
   int status = VIPERA_OK;
+  if (p.stage == 2) return launch_fold_any(p, s);
+  if (p.stage == 3) {
+    const long long values = static_cast<long long>(p.num_tokens) * p.heads * p.dv;
+    return vipera_launch(latent_gate_kernel<T>, static_cast<unsigned>((values + 255) / 256), 256, 0, s, p.o_heads, p.proj,
+                         p.proj_width, p.g_off, static_cast<T*>(p.out), p.num_tokens, p.heads, p.dv, p.padded_tokens);
+  }
   if (p.kv_off >= 0) {
     status = vipera_launch(latent_store_kernel<T>, p.num_tokens, 128, 0, s, p.proj, p.proj_width, p.kv_off, p.norm_weight,
                            p.eps, p.positions, p.cos_table, p.sin_table, static_cast<T*>(p.k_pool),
@@ -681,6 +782,10 @@ static int launch_latent(const LatentParams& p, cudaStream_t s) {
                            p.rot);
     if (status) return status;
   }
+  if (p.stage == 1)
+    return vipera_launch(latent_prep_kernel, p.num_tokens, 128, 0, s, p.proj, p.proj_width, p.q_off, p.positions, p.cos_table,
+                         p.sin_table, static_cast<__nv_bfloat16*>(p.a_heads), p.q_rot, p.tile_group, p.heads, p.d, p.rot,
+                         p.padded_tokens, p.scale);
   const dim3 tiles((p.num_tokens + kTile - 1) / kTile, p.heads);
   const dim3 absorb_grid(tiles.x, tiles.y, (p.rank + 127) / 128);
   status = vipera_launch(latent_absorb_kernel<T>, absorb_grid, 128, kTile * p.d * sizeof(float), s, p.proj, p.proj_width, p.q_off,
@@ -710,6 +815,13 @@ VIPERA_API int vipera_latent_attention(const LatentParams* params, int dtype, vo
   if (p.rank <= 0 || p.rank > kMaxRank || p.rot <= 0 || p.rot > kMaxRot || (p.rot & 1)) return VIPERA_BAD_SHAPE;
   if (p.heads <= 0 || p.d <= 0 || p.d > 1024 || p.dv <= 0 || p.page_size <= 0 || p.table_width <= 0) return VIPERA_BAD_SHAPE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (p.stage < 0 || p.stage > 3) return VIPERA_BAD_ARGUMENT;
+  if (p.stage != 0) {
+    if (dtype != VIPERA_BF16 || p.rank % 8 || p.rot % 8 || p.d % 8 || p.padded_tokens < p.num_tokens || p.padded_tokens % 128 ||
+        !p.a_heads || !p.qa_heads || !p.q_rot || !p.l_heads || !p.o_heads || !p.tile_group ||
+        p.num_tokens >= (1 << 24) / p.heads || (p.num_splits > 1 && p.split_keys % kFoldKeys))
+      return VIPERA_BAD_ARGUMENT;
+  }
   if (dtype == VIPERA_F32) return launch_latent<float>(p, s);
   if (dtype == VIPERA_BF16) return launch_latent<__nv_bfloat16>(p, s);
   return VIPERA_BAD_DTYPE;

@@ -1434,6 +1434,8 @@ class _LatentParams(ctypes.Structure):
         ("num_tokens", _c_int), ("heads", _c_int), ("d", _c_int), ("rot", _c_int), ("dv", _c_int), ("rank", _c_int),
         ("table_width", _c_int), ("page_size", _c_int), ("scale", _c_float), ("eps", _c_float),
         ("part", _c_void), ("split_keys", _c_int), ("num_splits", _c_int),
+        ("stage", _c_int), ("padded_tokens", _c_int), ("a_heads", _c_void), ("qa_heads", _c_void), ("q_rot", _c_void),
+        ("l_heads", _c_void), ("o_heads", _c_void), ("tile_group", _c_void),
     ]
 
 
@@ -1458,7 +1460,7 @@ def latent_attention(proj: torch.Tensor, *, q_off: int, g_off: int, kv_off: int,
                      block_table: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, k_pool: torch.Tensor,
                      v_pool: torch.Tensor, qa: torch.Tensor, latent_out: torch.Tensor, out: torch.Tensor, heads: int,
                      head_dim: int, rot_dim: int, value_dim: int, scale: float, max_keys: int = 0,
-                     part: Optional[torch.Tensor] = None) -> None:
+                     part: Optional[torch.Tensor] = None, head_major: Optional[dict] = None) -> None:
     """Causal softmax attention whose keys and values are products of a cached latent.  ``proj``
     float32 [tokens, width] holds q (head by head [head_dim | rot_dim]) at column ``q_off``, the
     output gate's pre-activation at ``g_off`` (negative: no gate) and the down projection
@@ -1469,7 +1471,13 @@ def latent_attention(proj: torch.Tensor, *, q_off: int, g_off: int, kv_off: int,
     transposed) are in the pools' type, as is ``out`` [tokens, heads * value_dim]; ``qa`` float32
     [tokens, heads, rank + rot_dim] and ``latent_out`` float32 [tokens, heads, rank] are scratch.
     ``max_keys`` (at least the longest history of the step) and ``part`` (float32,
-    latent_part_floats(...)) let a step of few tokens cut its keys between blocks."""
+    latent_part_floats(...)) let a step of few tokens cut its keys between blocks.  ``head_major``
+    (bfloat16): the products with the up matrices run as grouped tensor-core products, a head a
+    group, over rows padded to ``padded`` tokens per head: ``up_k_t`` [heads, rank, head_dim],
+    ``up_v_rows`` [heads, value_dim, rank] and the scratch ``a_heads`` (bfloat16 [heads * padded,
+    head_dim]), ``qa_heads`` (float32 [heads * padded, rank]), ``q_rot`` (float32 [tokens, heads *
+    rot_dim]), ``l_heads`` (bfloat16 [heads * padded, rank]), ``o_heads`` (float32 [heads * padded,
+    value_dim]) and ``tile_group`` (int32 [heads * padded / 128])."""
     fn = _function("latent", "vipera_latent_attention", [ctypes.POINTER(_LatentParams), _c_int, _c_void])
     _check_struct("latent", "vipera_latent_params_size", _LatentParams)
     tokens = proj.shape[0]
@@ -1510,6 +1518,29 @@ def latent_attention(proj: torch.Tensor, *, q_off: int, g_off: int, kv_off: int,
             if part.numel() < splits * tokens * heads * (rank + 2):
                 raise InvalidArgumentError("latent_attention: the scratch of the splits is too small")
             p.part, p.split_keys, p.num_splits = _gpu(part, "part", torch.float32), int(split_keys), int(splits)
+    if head_major is not None:
+        m = head_major
+        padded = int(m["padded"])
+        if padded % 128 or padded < tokens or tuple(m["up_k_t"].shape) != (heads, rank, head_dim) or \
+                tuple(m["up_v_rows"].shape) != (heads, value_dim, rank) or \
+                tuple(m["a_heads"].shape) != (heads * padded, head_dim) or tuple(m["qa_heads"].shape) != (heads * padded, rank) or \
+                tuple(m["l_heads"].shape) != (heads * padded, rank) or tuple(m["o_heads"].shape) != (heads * padded, value_dim) or \
+                m["q_rot"].numel() < tokens * heads * rot_dim or m["tile_group"].numel() < heads * padded // 128:
+            raise InvalidArgumentError("latent_attention: the head-major buffers do not match the step")
+        p.padded_tokens = padded
+        p.a_heads, p.l_heads = _gpu(m["a_heads"], "a_heads", torch.bfloat16), _gpu(m["l_heads"], "l_heads", torch.bfloat16)
+        p.qa_heads, p.q_rot = _gpu(m["qa_heads"], "qa_heads", torch.float32), _gpu(m["q_rot"], "q_rot", torch.float32)
+        p.o_heads, p.tile_group = _gpu(m["o_heads"], "o_heads", torch.float32), _gpu(m["tile_group"], "tile_group", torch.int32)
+        code = dtype_code(k_pool.dtype)
+        p.stage = 1
+        _check(fn(ctypes.byref(p), code, _stream()), "attention", kernels=2 if kv_off >= 0 else 1)
+        gemm_tc_grouped(m["a_heads"], m["up_k_t"], m["tile_group"], epilogue=EPI_STORE, out=m["qa_heads"], what="attention")
+        p.stage = 2
+        _check(fn(ctypes.byref(p), code, _stream()), "attention", kernels=2 if p.num_splits > 1 else 1)
+        gemm_tc_grouped(m["l_heads"], m["up_v_rows"], m["tile_group"], epilogue=EPI_STORE, out=m["o_heads"], what="attention")
+        p.stage = 3
+        _check(fn(ctypes.byref(p), code, _stream()), "attention")
+        return
     _check(fn(ctypes.byref(p), dtype_code(k_pool.dtype), _stream()), "attention", kernels=4 if kv_off >= 0 else 3)
 
 

@@ -30,6 +30,9 @@ from .base import Mixer, PagedKV
 from .linear import Linear
 
 
+HEAD_MAJOR_FROM = 64   # tokens of a step from which the up products run head by head on the tensor cores
+
+
 class LatentAttention(Mixer):
     """params: hidden_size, num_heads, head_dim (unrotated q/k values per head), rot_dim (rotated
     values per head; the key's are shared), value_dim, kv_rank, softmax_scale, norm_eps, position (a
@@ -79,6 +82,14 @@ class LatentAttention(Mixer):
         # each head's value matrix transposed, [heads, rank, value_dim]: neighbouring threads read neighbouring values
         self.up_v = tensors[f"{prefix}.uv.weight"].to(device=device, dtype=dtype).view(
             self.heads, self.vdim, self.rank).transpose(1, 2).contiguous()
+        # for long steps in bfloat16 both products run as grouped tensor-core products, a head a group:
+        # U_h transposed [heads, rank, d] and V_h as stored [heads, value_dim, rank]
+        self.head_major = (dtype == torch.bfloat16 and self.rank % 8 == 0 and self.rot % 8 == 0 and self.dim % 8 == 0)
+        self.up_k_t = self.up_v_rows = None
+        if self.head_major:
+            self.up_k_t = self.up_k.view(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
+            self.up_v_rows = tensors[f"{prefix}.uv.weight"].to(device=device, dtype=dtype).view(
+                self.heads, self.vdim, self.rank).contiguous()
         self.latent_norm = None
         if self.own_cache:
             self.latent_norm = tensors[f"{prefix}.dkv.norm.weight"].to(device=device, dtype=torch.float32).contiguous()
@@ -89,7 +100,8 @@ class LatentAttention(Mixer):
             raise UnsupportedError(f"{prefix}: the rotated part turns as interleaved pairs over all its {self.rot} values")
 
     def kernel_families(self):
-        return tuple(dict.fromkeys(("latent",) + self.proj.kernel_families() + self.out.kernel_families()))
+        grouped = ("gemm_tc",) if self.head_major else ()
+        return tuple(dict.fromkeys(("latent",) + grouped + self.proj.kernel_families() + self.out.kernel_families()))
 
     def prepare(self, max_positions: int) -> None:
         self.position.prepare(max_positions)
@@ -103,8 +115,10 @@ class LatentAttention(Mixer):
         heads, rank, r = params["num_heads"], params["kv_rank"], params["rot_dim"]
         width = heads * (params["head_dim"] + r + params["value_dim"]) + rank + r
         # (the splits of a step of few tokens: at most some 600 blocks of 16 rows more than the step's own)
+        padded = tokens + 127
+        head_major = heads * padded * (params["head_dim"] * 2 + rank * 6 + params["value_dim"] * 4) + tokens * heads * r * 4 + 4096
         return (tokens * (width * 4 + heads * (2 * rank + r) * 4 + heads * params["value_dim"] * element_bytes)
-                + 16 * (rank + 2) * 4 * 1300)
+                + 16 * (rank + 2) * 4 * 1300 + head_major)
 
     def forward(self, ctx, h, residual, cache, writes_cache):
         if writes_cache != self.own_cache:
@@ -119,12 +133,24 @@ class LatentAttention(Mixer):
         max_keys = max(int(ctx.max_kv_len), 1)
         floats = ops.latent_part_floats(count, self.heads, self.rank, max_keys, ops.sm_count(h.device)) if ctx.dtype == torch.bfloat16 else 0
         part = ws.get("latent.part", (floats,), torch.float32) if floats else None
+        head_major = None
+        if self.head_major and count >= HEAD_MAJOR_FROM:
+            padded = -(-count // 128) * 128
+            head_major = {
+                "padded": padded, "up_k_t": self.up_k_t, "up_v_rows": self.up_v_rows,
+                "a_heads": ws.get("latent.a_heads", (self.heads * padded, self.dim), torch.bfloat16),
+                "qa_heads": ws.get("latent.qa_heads", (self.heads * padded, self.rank), torch.float32),
+                "q_rot": ws.get("latent.q_rot", (count, self.heads * self.rot), torch.float32),
+                "l_heads": ws.get("latent.l_heads", (self.heads * padded, self.rank), torch.bfloat16),
+                "o_heads": ws.get("latent.o_heads", (self.heads * padded, self.vdim), torch.float32),
+                "tile_group": ws.get("latent.tile_group", (self.heads * padded // 128,), torch.int32),
+            }
         ops.latent_attention(proj, q_off=self.q_off, g_off=self.g_off, kv_off=self.kv_off, up_k=self.up_k, up_v=self.up_v,
                              norm_weight=self.latent_norm, eps=self.norm_eps, positions=ctx.positions,
                              token_entry=ctx.token_entry, block_table=ctx.block_tables[cache.group], cos=cos, sin=sin,
                              k_pool=cache.k, v_pool=cache.v, qa=qa, latent_out=mixed_latent, out=mixed, heads=self.heads,
                              head_dim=self.dim, rot_dim=self.rot, value_dim=self.vdim, scale=self.scale, max_keys=max_keys,
-                             part=part)
+                             part=part, head_major=head_major)
         self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
 
 
