@@ -53,8 +53,10 @@ group_rmsnorm_rows_kernel(const float* x, const float* __restrict__ weight, cons
   const float* w = weight + g * part;
   TO* dst = out + static_cast<size_t>(r) * hidden + g * part;
   float sum = 0.0f;
+#pragma unroll 4
   for (int i = lane; i < part; i += 32) sum += p[i] * p[i];
   const float inverse = 1.0f / sqrtf(warp_sum(sum) / static_cast<float>(part) + eps);
+#pragma unroll 4
   for (int i = lane; i < part; i += 32) dst[i] = from_float<TO>(p[i] * inverse * w[i]);
 }
 
@@ -63,7 +65,8 @@ VIPERA_API int vipera_group_rmsnorm(const float* x, const float* weight, const i
   if (num_rows <= 0) return VIPERA_OK;
   if (hidden <= 0 || groups <= 0 || hidden % groups) return VIPERA_BAD_SHAPE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool many = num_rows * groups >= 256 && hidden / groups <= 4096;
+  // (a warp per (row, group) for steps of every size: a row's sums then run in one order whatever the step holds)
+  const bool many = hidden / groups <= 4096;
   const int warps = kGroupThreads / 32;
   if (out_dtype == VIPERA_F32) {
     if (many)
@@ -99,6 +102,7 @@ gated_norm_add_kernel(float* __restrict__ branch, int parts, const float* __rest
   float* b = branch + static_cast<size_t>(r) * parts * hidden + g * part;
   const float* gt = gate ? gate + static_cast<size_t>(r) * hidden + g * part : nullptr;
   float sum = 0.0f;
+#pragma unroll 4
   for (int i = lane; i < part; i += 32) {
     float y = b[i];
     for (int p = 1; p < parts; ++p) y += b[static_cast<size_t>(p) * hidden + i];
@@ -109,6 +113,7 @@ gated_norm_add_kernel(float* __restrict__ branch, int parts, const float* __rest
   const float inverse = 1.0f / sqrtf(warp_sum(sum) / static_cast<float>(part) + eps);
   float* dst = residual + static_cast<size_t>(r) * hidden + g * part;
   const float* c = coef + g * part;
+#pragma unroll 4
   for (int i = lane; i < part; i += 32) dst[i] += c[i] * (b[i] * inverse);
 }
 
