@@ -77,23 +77,37 @@ __device__ __forceinline__ void warp_argmax(float& best, int& index) {
 template <typename T>
 __global__ void __launch_bounds__(kRouteThreads)
 moe_route_kernel(MoeParams p) {
-  extern __shared__ float route_shared[];
+  extern __shared__ __align__(16) float route_shared[];
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
-  float* score = route_shared;
+  float* h_s = route_shared;                // [hidden] (first: read as vectors)
+  float* score = h_s + p.hidden;
   float* open = score + p.experts;          // the score while the expert may still be chosen, else -inf
   float* group_score = open + p.experts;
-  float* h_s = group_score + p.groups;      // [hidden]
   const T* h = static_cast<const T*>(p.h) + static_cast<size_t>(t) * p.hidden;
   for (int i = threadIdx.x; i < p.hidden; i += kRouteThreads) h_s[i] = to_float<T>(h[i]);
   __syncthreads();
   for (int e = warp; e < p.experts; e += kRouteThreads / 32) {
     const float* r = p.router + static_cast<size_t>(e) * p.hidden;
     float sum = 0.0f;
+    if ((p.hidden & 3) == 0 && (reinterpret_cast<uintptr_t>(p.router) & 15) == 0) {
+      // four values at a time: a lane sums the products of values 4 (lane + 32 j) .. + 3, in that order
+      const float4* r4 = reinterpret_cast<const float4*>(r);
+      const float4* h4 = reinterpret_cast<const float4*>(h_s);
 #pragma unroll 4
-    for (int i = lane; i < p.hidden; i += 32) sum = fmaf(h_s[i], r[i], sum);
+      for (int i = lane; i < p.hidden / 4; i += 32) {
+        const float4 a = h4[i], b = r4[i];
+        sum = fmaf(a.x, b.x, sum);
+        sum = fmaf(a.y, b.y, sum);
+        sum = fmaf(a.z, b.z, sum);
+        sum = fmaf(a.w, b.w, sum);
+      }
+    } else {
+#pragma unroll 4
+      for (int i = lane; i < p.hidden; i += 32) sum = fmaf(h_s[i], r[i], sum);
+    }
     sum = warp_sum(sum);
     if (lane == 0) score[e] = sum;
   }
