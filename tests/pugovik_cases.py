@@ -63,12 +63,21 @@ ODD = config([latent_layer(heads=1, dim=6, rot_dim=10, vdim=7, rank=19, scale=0.
               lightning_layer(heads=2, dim=37, vdim=5, decay=(0.0, 0.5)),
               latent_layer(heads=2, dim=5, rot_dim=10, vdim=9, rank=19, scale=0.4, scaling=False, kv_from=0)],
              width=100, vocab=97, eps=1e-4, groups=1, mult=1.0)
+# A larger one for long steps: a latent that is no multiple of 16, more heads, many experts in groups, a
+# layer that reads the first layer's pages with other heads, a last layer without a feed-forward.
+LARGE = config([latent_layer(heads=8, dim=32, rot_dim=16, vdim=48, rank=136, scale=0.11, base=20000.0,
+                             mlp=moe(ff=112, experts=32, top=6, groups=8, keep=3)),
+                lightning_layer(heads=4, dim=48, vdim=96, decay=(0.6, 0.9, 0.99, 0.9995), mlp=moe(ff=64, experts=4, top=2, groups=2, keep=2)),
+                latent_layer(heads=4, dim=16, rot_dim=16, vdim=32, rank=136, scale=0.2, base=20000.0, kv_from=0,
+                             mlp=moe(ff=48, experts=6, top=1, groups=3, keep=2)),
+                lightning_layer(heads=2, dim=64, vdim=64, decay=(0.97, 0.5))],
+               width=384, vocab=1000, eps=1e-5, groups=2, mult=0.9)
 ONLY_LATENT = config([latent_layer()])
 ONLY_SHARED = config([latent_layer(), latent_layer(heads=2, dim=12, vdim=10, scale=0.4, kv_from=0)])
 ONLY_LIGHTNING = config([lightning_layer()])
 ONLY_MOE = config([lightning_layer(heads=1, dim=4, vdim=4, decay=(0.5,), mlp=moe(ff=32, experts=12, top=3, groups=4, keep=2))])
 
-CONFIGS = {"mixed": MIXED, "wide": WIDE, "odd": ODD, "latent": ONLY_LATENT, "shared": ONLY_SHARED,
+CONFIGS = {"mixed": MIXED, "wide": WIDE, "odd": ODD, "large": LARGE, "latent": ONLY_LATENT, "shared": ONLY_SHARED,
            "lightning": ONLY_LIGHTNING, "moe": ONLY_MOE}
 
 # How stored tensors are changed (by the end of their names): ("mul", x) or ("add", x).

@@ -40,8 +40,8 @@ class Judge:
     router's choice hangs on less than CLOSE_CALL (`margins`) may come out with other experts: it
     must be finite, and is left out of the statistics; few positions may be such."""
 
-    def __init__(self, dtype, want_all, margins=None):
-        self.dtype, self.want_all = dtype, want_all
+    def __init__(self, dtype, want_all, margins=None, most_skipped=0.4):
+        self.dtype, self.want_all, self.most_skipped = dtype, want_all, most_skipped
         self.close_call = None if margins is None else np.asarray(margins) < CLOSE_CALL
         self.scale = float(np.abs(want_all).max())
         centred = np.asarray(want_all, dtype=np.float64)
@@ -74,7 +74,7 @@ class Judge:
     def close(self):
         if self.dtype == "float32":
             return
-        assert self.errors and self.skipped <= 0.4 * (self.skipped + len(self.errors)), (self.skipped, len(self.errors))
+        assert self.errors and self.skipped <= self.most_skipped * (self.skipped + len(self.errors)), (self.skipped, len(self.errors))
         errors = np.sort(np.asarray(self.errors))
         median, most, worst = np.median(errors), errors[int(0.95 * (len(errors) - 1))], errors[-1]
         tipped = int((errors > BF16_FEW).sum())
@@ -137,6 +137,40 @@ def test_prompt_against_decoding_and_portions(name, dtype):
         done += size
     judge.close()
     assert done == length and rp.pools.audit() == ""
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_steps_of_a_larger_model(dtype):
+    """Steps of hundreds of tokens (the forms of the kernels that long steps take): two requests of
+    unequal length in one step, then portions of one beside single tokens of the other, then both
+    token by token."""
+    path = folder_for("large", dtype, sharp="mild")
+    vocab = cases.CONFIGS["large"]["vocab"]
+    long, short = helpers.random_tokens(vocab, 760, 3), helpers.random_tokens(vocab, 150, 4)
+    want = {"long": cases.plain_logits(path, long), "short": cases.plain_logits(path, short)}
+    # (32 experts of which 6 are taken: more choices hang on a hair than in the smaller models)
+    judges = {name: Judge(dtype, want[name], cases.plain_margins(path, tokens), most_skipped=0.6)
+              for name, tokens in (("long", long), ("short", short))}
+    rp = replayer(path, dtype, 768 + 192, page_size=16)
+    got = rp.step([{"id": "long", "tokens": long[:650], "want": list(range(0, 650, 7))},
+                   {"id": "short", "tokens": short[:131], "want": list(range(131))}], [])
+    rows = len(range(0, 650, 7))
+    for row, position in enumerate(range(0, 650, 7)):
+        judges["long"].add(got[row], want["long"][position], ("long", position))
+    judges["short"].add(got[rows:], want["short"][:131], "short")
+    got = rp.step([{"id": "long", "tokens": long[650:745], "want": list(range(95))},
+                   {"id": "short", "tokens": short[131:132], "want": [0]}], [])
+    judges["long"].add(got[:95], want["long"][650:745], "long portion")
+    judges["short"].add(got[95], want["short"][131], "short single")
+    for step in range(15):
+        got = rp.step([{"id": "long", "tokens": long[745 + step:746 + step], "want": [0]},
+                       {"id": "short", "tokens": short[132 + step:133 + step], "want": [0]}],
+                      ["long", "short"] if step == 14 else [])
+        judges["long"].add(got[0], want["long"][745 + step], ("long", step))
+        judges["short"].add(got[1], want["short"][132 + step], ("short", step))
+    for judge in judges.values():
+        judge.close()
+    assert rp.pools.audit() == ""
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -449,6 +483,8 @@ FOLDS = {
     "small": ((3, 16, 8, 8, 40), [(0, 70), (33, 2), (200, 1), (0, 1), (5, 11)]),
     "many_heads": ((20, 8, 24, 16, 136), [(90, 3), (300, 1), (0, 9)]),
     "long_prompts": ((3, 16, 8, 8, 40), [(0, 903), (37, 650)]),   # enough rows for blocks of two groups of sixteen
+    "mid_rank": ((4, 16, 16, 16, 200), [(0, 300), (45, 7)]),
+    "mid_rank_long": ((8, 8, 8, 8, 136), [(3, 500), (0, 210)]),
 }
 
 
