@@ -10,6 +10,7 @@
 #include "common.cuh"
 
 constexpr int kGroupThreads = 256;
+constexpr int kKeep = 32;   // values of a group a lane keeps in registers between its two passes (groups up to 1,024 values)
 
 // One block per output row.  A thread reads the same elements in both passes and writes them only in
 // the second, so `out` may be `x` itself (32-bit, rows == nullptr).
@@ -53,6 +54,23 @@ group_rmsnorm_rows_kernel(const float* x, const float* __restrict__ weight, cons
   const float* w = weight + g * part;
   TO* dst = out + static_cast<size_t>(r) * hidden + g * part;
   float sum = 0.0f;
+  if (part <= 32 * kKeep) {
+    // the lane's values stay in registers between the passes: no load waits behind a store
+    float kept[kKeep];
+#pragma unroll
+    for (int j = 0; j < kKeep; ++j) {
+      const int i = lane + 32 * j;
+      kept[j] = i < part ? p[i] : 0.0f;
+      sum += kept[j] * kept[j];
+    }
+    const float inverse = 1.0f / sqrtf(warp_sum(sum) / static_cast<float>(part) + eps);
+#pragma unroll
+    for (int j = 0; j < kKeep; ++j) {
+      const int i = lane + 32 * j;
+      if (i < part) dst[i] = from_float<TO>(kept[j] * inverse * w[i]);
+    }
+    return;
+  }
 #pragma unroll 4
   for (int i = lane; i < part; i += 32) sum += p[i] * p[i];
   const float inverse = 1.0f / sqrtf(warp_sum(sum) / static_cast<float>(part) + eps);
@@ -102,7 +120,6 @@ gated_norm_add_kernel(float* __restrict__ branch, int parts, const float* __rest
   float* b = branch + static_cast<size_t>(r) * parts * hidden + g * part;
   const float* gt = gate ? gate + static_cast<size_t>(r) * hidden + g * part : nullptr;
   float sum = 0.0f;
-#pragma unroll 4
   for (int i = lane; i < part; i += 32) {
     float y = b[i];
     for (int p = 1; p < parts; ++p) y += b[static_cast<size_t>(p) * hidden + i];
@@ -113,7 +130,6 @@ gated_norm_add_kernel(float* __restrict__ branch, int parts, const float* __rest
   const float inverse = 1.0f / sqrtf(warp_sum(sum) / static_cast<float>(part) + eps);
   float* dst = residual + static_cast<size_t>(r) * hidden + g * part;
   const float* c = coef + g * part;
-#pragma unroll 4
   for (int i = lane; i < part; i += 32) dst[i] += c[i] * (b[i] * inverse);
 }
 
