@@ -510,33 +510,52 @@ latent_fold_kernel(LatentFoldParams p) {
 }
 
 // out[row, :] = sum_s e^(m_s - m) columns_s / sum_s e^(m_s - m) sum_s over the splits that saw a key.
+// The splits' maxima and sums are read side by side (a thread a split), the weights e^(m_s - m) / total
+// kept in shared memory, and a column's terms asked for four splits at a time, added in the splits' order.
+constexpr int kMostSplits = 64;
+
 __global__ void __launch_bounds__(128)
 latent_combine_kernel(LatentFoldParams p) {
+  __shared__ float top_s[kMostSplits], sum_s[kMostSplits], weight_s[kMostSplits];
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x;
   const size_t rows = static_cast<size_t>(p.num_tokens) * p.heads, each = p.rank + 2;
-  float top = -INFINITY;
-  for (int s = 0; s < p.num_splits; ++s) {
-    const float* part = p.part + (s * rows + row) * each;
-    if (part[p.rank + 1] > 0.0f) top = fmaxf(top, part[p.rank]);
+  const float* first = p.part + static_cast<size_t>(row) * each;
+  if (threadIdx.x < p.num_splits) {
+    const float* part = first + threadIdx.x * rows * each;
+    top_s[threadIdx.x] = part[p.rank];
+    sum_s[threadIdx.x] = part[p.rank + 1];
   }
-  float total = 0.0f;
-  for (int s = 0; s < p.num_splits; ++s) {
-    const float* part = p.part + (s * rows + row) * each;
-    if (part[p.rank + 1] > 0.0f) total += part[p.rank + 1] * expf(part[p.rank] - top);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float top = -INFINITY, total = 0.0f;
+    for (int s = 0; s < p.num_splits; ++s)
+      if (sum_s[s] > 0.0f) top = fmaxf(top, top_s[s]);
+    for (int s = 0; s < p.num_splits; ++s) {
+      weight_s[s] = sum_s[s] > 0.0f ? expf(top_s[s] - top) : 0.0f;
+      total += sum_s[s] * weight_s[s];
+    }
+    const float inverse = 1.0f / total;
+    for (int s = 0; s < p.num_splits; ++s) weight_s[s] *= inverse;
   }
-  const float inverse = 1.0f / total;
+  __syncthreads();
   for (int c = threadIdx.x; c < p.rank; c += blockDim.x) {
     float sum = 0.0f;
-    for (int s = 0; s < p.num_splits; ++s) {
-      const float* part = p.part + (s * rows + row) * each;
-      if (part[p.rank + 1] > 0.0f) sum += part[c] * expf(part[p.rank] - top);
+    int s = 0;
+    for (; s + 4 <= p.num_splits; s += 4) {
+      const float v0 = first[(s * rows) * each + c], v1 = first[((s + 1) * rows) * each + c];
+      const float v2 = first[((s + 2) * rows) * each + c], v3 = first[((s + 3) * rows) * each + c];
+      sum = fmaf(v0, weight_s[s], sum);
+      sum = fmaf(v1, weight_s[s + 1], sum);
+      sum = fmaf(v2, weight_s[s + 2], sum);
+      sum = fmaf(v3, weight_s[s + 3], sum);
     }
+    for (; s < p.num_splits; ++s) sum = fmaf(first[(s * rows) * each + c], weight_s[s], sum);
     if (p.l_heads != nullptr)
-      p.l_heads[(static_cast<size_t>(row % p.heads) * p.padded_tokens + row / p.heads) * p.rank + c] = __float2bfloat16(sum * inverse);
+      p.l_heads[(static_cast<size_t>(row % p.heads) * p.padded_tokens + row / p.heads) * p.rank + c] = __float2bfloat16(sum);
     else
-      p.out[static_cast<size_t>(row) * p.rank + c] = sum * inverse;
+      p.out[static_cast<size_t>(row) * p.rank + c] = sum;
   }
 }
 
@@ -748,6 +767,7 @@ static int launch_fold_any(const LatentParams& p, cudaStream_t s) {
   f.tokens_per_tile = kFoldRows * groups / f.head_group;
   f.num_splits = p.num_splits > 1 && p.part ? p.num_splits : 1;
   f.split_keys = f.num_splits > 1 ? p.split_keys : 0x3fffffff;
+  if (f.num_splits > kMostSplits) return VIPERA_BAD_ARGUMENT;
   const int rank_pad = round_up(p.rank, 16);
   const int stride = round_up(rank_pad + round_up(p.rot, 16), 32) + 8;
   const int rows = kFoldRows * groups;
