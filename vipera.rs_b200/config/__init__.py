@@ -22,6 +22,7 @@ from .qwen2 import Qwen2Config, qwen2_model_spec
 from .nobupel import NobupelConfig, nobupel_model_spec
 from .gusolix import GusolixConfig, gusolix_model_spec
 from .pugovik import PugovikConfig, pugovik_model_spec
+from .fasolorn import FasolornConfig, fasolorn_model_spec
 
 
 def read_config_json(model_dir: str) -> Dict[str, Any]:
@@ -66,6 +67,6 @@ __all__ = [
     "Architecture", "Registry", "register_architecture",
     "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry",
     "Qwen2Config", "qwen2_model_spec", "NobupelConfig", "nobupel_model_spec", "GusolixConfig", "gusolix_model_spec",
-    "PugovikConfig", "pugovik_model_spec",
+    "PugovikConfig", "pugovik_model_spec", "FasolornConfig", "fasolorn_model_spec",
     "read_config_json", "architecture_of", "load_config",
 ]

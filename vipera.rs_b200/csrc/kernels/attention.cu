@@ -15,7 +15,10 @@
 // later query, at their true positions; and a sink, an extra key of score 0 without a value,
 // which adds exp(0 - max) to the softmax's denominator (p_j = e^{s_j} / (1 + sum e^{s_j})).
 // Instead of a window the mask may be one of chunks (`chunk`): position i sees j <= i with
-// floor(i / chunk) = floor(j / chunk).  `out_scale` multiplies the output.
+// floor(i / chunk) = floor(j / chunk).  `out_scale` multiplies the output.  The sink's score may be
+// learned, one per query head (`sink_values`: exp(sink_h - max) joins the denominator, unscaled), and
+// the output may be gated: out[t, h, e] *= sigmoid(gate[t * gate_stride + h * value_dim + e]), the gate
+// a 32-bit pre-activation.
 //
 // This kernel is the attention of the 32-bit path and takes every head size that is a
 // up to 256 (keys and values each; sizes that are not a multiple of 8 are read value by value), any number of heads and groups, any page size.
@@ -72,7 +75,8 @@ attention_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restri
                  const T* __restrict__ v_pool, const int* __restrict__ token_seq,
                  const int* __restrict__ positions, const int* __restrict__ block_table, int table_width,
                  int page_size, int num_heads, int num_kv_heads, int head_dim, int value_dim, float scale,
-                 int window, int keep_first, int sink, int chunk, float out_scale) {
+                 int window, int keep_first, int sink, int chunk, float out_scale,
+                 const float* __restrict__ sink_values, const float* __restrict__ gate, long long gate_stride) {
   __shared__ float q_shared[kWarpsPerBlock][kMaxHeadDim];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -134,20 +138,26 @@ attention_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restri
     }
   }
   }
-  if (sink) {
-    // the sink's score is 0: fold it in like one more key whose value is zero
-    const float new_max = fmaxf(running_max, 0.0f);
+  if (sink || sink_values) {
+    // the sink's score is 0 (or the head's learned one): fold it in like one more key whose value is zero
+    const float sink_score = sink_values ? sink_values[h] : 0.0f;
+    const float new_max = fmaxf(running_max, sink_score);
     const float alpha = expf(running_max - new_max);
-    running_sum = running_sum * alpha + expf(0.0f - new_max);
+    running_sum = running_sum * alpha + expf(sink_score - new_max);
 #pragma unroll
     for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] *= alpha;
   }
   const float inverse = out_scale / running_sum;
   T* out_row = out + (static_cast<size_t>(t) * num_heads + h) * value_dim;
+  const float* gate_row = gate ? gate + static_cast<size_t>(t) * gate_stride + static_cast<size_t>(h) * value_dim : nullptr;
 #pragma unroll
   for (int i = 0; i < kMaxHeadDim / 32; ++i) {
     const int e = lane + 32 * i;
-    if (e < value_dim) out_row[e] = from_float<T>(acc[i] * inverse);
+    if (e < value_dim) {
+      float value = acc[i] * inverse;
+      if (gate_row) value *= 1.0f / (1.0f + expf(-gate_row[e]));
+      out_row[e] = from_float<T>(value);
+    }
   }
 }
 
@@ -157,11 +167,14 @@ attention_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restri
 // positions[t] its position.  The keys and values of this step's tokens must already be
 // in the cache.  window = 0 means every earlier key is visible; keep_first counts only with a
 // window; sink != 0 adds the sink to the denominator.
-VIPERA_API int vipera_attention(const void* q, void* out, int dtype, const void* k_pool, const void* v_pool,
-                                const int* token_seq, const int* positions, const int* block_table,
-                                int table_width, int page_size, int num_tokens, int num_heads,
-                                int num_kv_heads, int head_dim, int value_dim, float scale, int window,
-                                int keep_first, int sink, int chunk, float out_scale, void* stream) {
+// sink_values (null: none) holds a learned sink score per query head; gate (null: none) the output
+// gate's 32-bit pre-activations, row t at gate + t * gate_stride, [heads * value_dim] values.
+VIPERA_API int vipera_attention_gated(const void* q, void* out, int dtype, const void* k_pool, const void* v_pool,
+                                      const int* token_seq, const int* positions, const int* block_table,
+                                      int table_width, int page_size, int num_tokens, int num_heads,
+                                      int num_kv_heads, int head_dim, int value_dim, float scale, int window,
+                                      int keep_first, int sink, int chunk, float out_scale, const float* sink_values,
+                                      const float* gate, long long gate_stride, void* stream) {
   if (num_tokens <= 0) return VIPERA_OK;
   if (chunk < 0 || (chunk > 0 && window > 0)) return VIPERA_BAD_ARGUMENT;
   if (head_dim <= 0 || head_dim > kMaxHeadDim) return VIPERA_BAD_SHAPE;
@@ -174,16 +187,27 @@ VIPERA_API int vipera_attention(const void* q, void* out, int dtype, const void*
     attention_kernel<float><<<grid, kWarpsPerBlock * 32, 0, s>>>(
         static_cast<const float*>(q), static_cast<float*>(out), static_cast<const float*>(k_pool),
         static_cast<const float*>(v_pool), token_seq, positions, block_table, table_width, page_size,
-        num_heads, num_kv_heads, head_dim, value_dim, scale, window, keep_first, sink, chunk, out_scale);
+        num_heads, num_kv_heads, head_dim, value_dim, scale, window, keep_first, sink, chunk, out_scale, sink_values,
+        gate, gate_stride);
   else if (dtype == VIPERA_BF16)
     attention_kernel<__nv_bfloat16><<<grid, kWarpsPerBlock * 32, 0, s>>>(
         static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out),
         static_cast<const __nv_bfloat16*>(k_pool), static_cast<const __nv_bfloat16*>(v_pool), token_seq,
         positions, block_table, table_width, page_size, num_heads, num_kv_heads, head_dim, value_dim, scale, window,
-        keep_first, sink, chunk, out_scale);
+        keep_first, sink, chunk, out_scale, sink_values, gate, gate_stride);
   else
     return VIPERA_BAD_DTYPE;
   return vipera_launch_status();
+}
+
+VIPERA_API int vipera_attention(const void* q, void* out, int dtype, const void* k_pool, const void* v_pool,
+                                const int* token_seq, const int* positions, const int* block_table,
+                                int table_width, int page_size, int num_tokens, int num_heads,
+                                int num_kv_heads, int head_dim, int value_dim, float scale, int window,
+                                int keep_first, int sink, int chunk, float out_scale, void* stream) {
+  return vipera_attention_gated(q, out, dtype, k_pool, v_pool, token_seq, positions, block_table, table_width, page_size,
+                                num_tokens, num_heads, num_kv_heads, head_dim, value_dim, scale, window, keep_first, sink,
+                                chunk, out_scale, nullptr, nullptr, 0, stream);
 }
 
 VIPERA_API const char* vipera_attention_status_text(int status) { return vipera_status_text(status); }

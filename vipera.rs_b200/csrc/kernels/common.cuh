@@ -36,12 +36,16 @@ __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
-// Activations of a gated unit's gate.
-enum ViperaActivation { ACT_SILU = 0, ACT_GELU_TANH = 1 };
+// Activations of a gated unit's gate, or of a unit without a gate.
+enum ViperaActivation { ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_RELU2 = 2 };
 
 __device__ __forceinline__ float gate_activation(float z, int activation) {
   if (activation == ACT_GELU_TANH)
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  if (activation == ACT_RELU2) {   // the square of relu
+    const float r = fmaxf(z, 0.0f);
+    return r * r;
+  }
   return z / (1.0f + expf(-z));
 }
 

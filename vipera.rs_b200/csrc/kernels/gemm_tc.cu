@@ -354,7 +354,9 @@ __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v
         if constexpr (EXT) p.resid[at] += v[i] + (p.bias ? p.bias[n] : 0.0f);
         else p.resid[at] += v[i];
       } else {
-        const float value = v[i] + (p.bias ? p.bias[n] : 0.0f);
+        float value = v[i] + (p.bias ? p.bias[n] : 0.0f);
+        // the plain store of a unit without a gate: its activation on the way out
+        if constexpr (EXT) if (p.activation == ACT_RELU2) value = gate_activation(value, ACT_RELU2);
         if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
         else static_cast<float*>(p.out)[at] = value;
       }
@@ -1736,11 +1738,16 @@ VIPERA_API int vipera_gemm_tc_act(const void* A, const void* W, int T, int N, in
 
 // Grouped: W is [groups, N, K]; A is [T, K] with T a multiple of 128, and rows 128 * i .. 128 * i + 127
 // are multiplied by matrix tile_group[i] (a device table that a kernel ahead in the stream writes).
-// Endings STORE and the gated unit.
+// Endings STORE and the gated unit; STORE into bfloat16 with activation ACT_RELU2 applies the square of
+// relu on the way out (a unit without a gate).
 VIPERA_API int vipera_gemm_tc_grouped(const void* A, const void* W, int T, int N, int K, int groups, const int* tile_group,
                                       int epilogue, void* out, int out_dtype, int activation, int* status, void* stream) {
   if (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) return VIPERA_BAD_ARGUMENT;
-  if (activation != ACT_SILU && activation != ACT_GELU_TANH) return VIPERA_BAD_ARGUMENT;
+  if (activation == ACT_RELU2) {
+    if (epilogue != EPI_STORE || out_dtype != VIPERA_BF16) return VIPERA_BAD_ARGUMENT;
+  } else if (activation != ACT_SILU && activation != ACT_GELU_TANH) {
+    return VIPERA_BAD_ARGUMENT;
+  }
   if (!tile_group) return VIPERA_BAD_ARGUMENT;
   return run_gemm(A, W, T, N, K, epilogue, nullptr, out, out_dtype, nullptr, nullptr, 0, status, stream, nullptr, activation,
                   tile_group, groups);

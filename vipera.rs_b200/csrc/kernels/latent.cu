@@ -12,12 +12,19 @@
 //
 // so the keys and values of earlier tokens are never expanded.  Scores, softmax, the sums over
 // keys, the latent's norm and the rotation are 32-bit.  Rotation: values (2i, 2i + 1) of the
-// rotated part turn by the angle whose cosine and sine the tables hold at [position, i].
+// rotated part (`pairing` 0) or values (i, i + rot/2) (`pairing` 1) turn by the angle whose cosine
+// and sine the tables hold at [position, i].  With a window w > 0 the query at position p sees keys
+// p - w + 1 .. p only; earlier keys' pages may have been given back and are never read.
 #include "attention_mma.cuh"
 
 constexpr int kMaxRank = 512;   // latent size
 constexpr int kMaxRot = 128;    // rotated part
 constexpr int kWarps = 4;
+
+// The two values of the rotated part that turn together as pair i.
+__device__ __forceinline__ void rot_pair(int pairing, int rot, int i, int& a, int& b) {
+  if (pairing) { a = i; b = i + rot / 2; } else { a = 2 * i; b = 2 * i + 1; }
+}
 
 // ---------------------------------------------------------------------------------------
 // The step's latents and rotated key parts into their pages.  `proj` [tokens, proj_width] holds
@@ -30,7 +37,7 @@ latent_store_kernel(const float* __restrict__ proj, long long proj_width, int kv
                     float eps, const int* __restrict__ positions, const float* __restrict__ cos_table,
                     const float* __restrict__ sin_table, T* __restrict__ k_pool, T* __restrict__ v_pool,
                     const int* __restrict__ token_entry, const int* __restrict__ block_table, int table_width,
-                    int page_size, int rank, int rot) {
+                    int page_size, int rank, int rot, int pairing) {
   __shared__ float scratch[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -48,9 +55,11 @@ latent_store_kernel(const float* __restrict__ proj, long long proj_width, int kv
   const float* cs = cos_table + static_cast<size_t>(position) * (rot / 2);
   const float* sn = sin_table + static_cast<size_t>(position) * (rot / 2);
   for (int i = threadIdx.x; i < rot / 2; i += blockDim.x) {
-    const float u = row[rank + 2 * i], v = row[rank + 2 * i + 1];
-    r_row[2 * i] = from_float<T>(u * cs[i] - v * sn[i]);
-    r_row[2 * i + 1] = from_float<T>(v * cs[i] + u * sn[i]);
+    int ia, ib;
+    rot_pair(pairing, rot, i, ia, ib);
+    const float u = row[rank + ia], v = row[rank + ib];
+    r_row[ia] = from_float<T>(u * cs[i] - v * sn[i]);
+    r_row[ib] = from_float<T>(v * cs[i] + u * sn[i]);
   }
 }
 
@@ -66,7 +75,7 @@ __global__ void __launch_bounds__(128)
 latent_absorb_kernel(const float* __restrict__ proj, long long proj_width, int q_off, const TW* __restrict__ up_k,
                      const int* __restrict__ positions, const float* __restrict__ cos_table,
                      const float* __restrict__ sin_table, float* __restrict__ qa, int num_tokens, int heads, int d,
-                     int rank, int rot, float scale) {
+                     int rank, int rot, float scale, int pairing) {
   extern __shared__ float q_tile[];   // [kTile][d]
   pdl_launch_dependents();
   pdl_wait();
@@ -102,10 +111,12 @@ latent_absorb_kernel(const float* __restrict__ proj, long long proj_width, int q
     const int position = positions[t];
     const float c = cos_table[static_cast<size_t>(position) * (rot / 2) + pair];
     const float s = sin_table[static_cast<size_t>(position) * (rot / 2) + pair];
-    const float a = q_rot[2 * pair], b = q_rot[2 * pair + 1];
+    int ia, ib;
+    rot_pair(pairing, rot, pair, ia, ib);
+    const float a = q_rot[ia], b = q_rot[ib];
     float* dst = qa + (static_cast<size_t>(t) * heads + h) * (rank + rot) + rank;
-    dst[2 * pair] = (a * c - b * s) * scale;
-    dst[2 * pair + 1] = (b * c + a * s) * scale;
+    dst[ia] = (a * c - b * s) * scale;
+    dst[ib] = (b * c + a * s) * scale;
   }
 }
 
@@ -163,7 +174,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 latent_attention_kernel(const float* __restrict__ qa, float* __restrict__ mixed, const T* __restrict__ k_pool,
                         const T* __restrict__ v_pool, const int* __restrict__ token_entry,
                         const int* __restrict__ positions, const int* __restrict__ block_table, int table_width,
-                        int page_size, int heads, int rank, int rot) {
+                        int page_size, int heads, int rank, int rot, int window) {
   extern __shared__ float q_shared[];   // [kWarps][rank + rot]
   pdl_launch_dependents();
   pdl_wait();
@@ -183,7 +194,7 @@ latent_attention_kernel(const float* __restrict__ qa, float* __restrict__ mixed,
 #pragma unroll
   for (int i = 0; i < kMaxRank / 32; ++i) acc[i] = 0.0f;
   float running_max = -INFINITY, running_sum = 0.0f;
-  for (int base = 0; base <= position; base += 32) {
+  for (int base = window > 0 ? max(0, position - window + 1) : 0; base <= position; base += 32) {
     const int j = base + lane;
     const bool valid = j <= position;
     float score = -INFINITY;
@@ -249,6 +260,7 @@ struct LatentFoldParams {
   float* part;                     // splits: [num_splits][tokens * heads][rank + 2]: columns, then m and sum
   int num_tokens, heads, rank, rot, table_width, page_size;
   int head_group, tokens_per_tile, split_keys, num_splits;
+  int window;                      // > 0: a row at position p sees keys p - window + 1 .. p
   // Head-major form (the products on both sides of the fold run as grouped tensor-core products, a
   // head a group): the unrotated part of qa comes unscaled from qa_heads [heads, padded_tokens, rank]
   // and the rotated, scaled part from q_rot [tokens, heads, rot]; the folded latents leave as
@@ -301,13 +313,16 @@ latent_fold_kernel(LatentFoldParams p) {
       if (t0 + tq < p.num_tokens && !((done >> tq) & 1u)) { lead = tq; break; }
     if (lead < 0) break;
     const int entry = p.token_entry[t0 + lead];
-    int last_key = -1;
+    int last_key = -1, first_key = 0x7fffffff;
     unsigned taken = 0;
     for (int tq = lead; tq < p.tokens_per_tile && t0 + tq < p.num_tokens; ++tq)
       if (!((done >> tq) & 1u) && p.token_entry[t0 + tq] == entry) {
         taken |= 1u << tq;
         last_key = max(last_key, p.positions[t0 + tq]);
+        first_key = min(first_key, p.positions[t0 + tq]);
       }
+    // the first key any of the pass's rows sees: nothing before it is read (its page may be gone)
+    first_key = p.window > 0 ? max(0, first_key - p.window + 1) : 0;
     __syncthreads();   // the pass before is done with the rows' tables
     if (threadIdx.x < kRows) {
       const int r = threadIdx.x, tq = r / p.head_group, head = head0 + r % p.head_group;
@@ -334,8 +349,11 @@ latent_fold_kernel(LatentFoldParams p) {
       }
       q_s[r * stride + (c < p.rank ? c : rank_pad + c - p.rank)] = __float2bfloat16(v);
     }
-    const int begin = split * p.split_keys;
-    const int end = min(last_key + 1, begin + p.split_keys);
+    // tiles are counted from the split's first key, whatever the window: the first tile that holds a
+    // visible key is the first one folded
+    const int split_begin = split * p.split_keys;
+    const int begin = split_begin + max(0, first_key - split_begin) / kFoldKeys * kFoldKeys;
+    const int end = min(last_key + 1, split_begin + p.split_keys);
     const int num_tiles = end > begin ? (end - begin + kFoldKeys - 1) / kFoldKeys : 0;
     const int* table = p.block_table + static_cast<size_t>(entry) * p.table_width;
 
@@ -347,12 +365,12 @@ latent_fold_kernel(LatentFoldParams p) {
       size_t slots[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const int key = min(key0 + i, end - 1);
+        const int key = max(min(key0 + i, end - 1), first_key);
         slots[i] = static_cast<size_t>(table[key / p.page_size]) * p.page_size + key % p.page_size;
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const bool valid = key0 + i < end;
+        const bool valid = key0 + i < end && key0 + i >= first_key;
         const __nv_bfloat16* c_row = p.k_pool + slots[i] * p.rank;
         const __nv_bfloat16* r_row = p.v_pool + slots[i] * p.rot;
         __nv_bfloat16* dst = dst_tile + (warp * 8 + i) * stride;
@@ -409,7 +427,8 @@ latent_fold_kernel(LatentFoldParams p) {
           for (int e = 0; e < 4; ++e) {
             const int row = mt * kFoldRows + g + (e >> 1) * 8, col = warp * 8 + pair + (e & 1);
             const int key = key0 + col;
-            s_s[row * kScoreStride + col] = (key <= limit_s[row] && key < end) ? c[mt][e] + c_odd[mt][e] : -INFINITY;
+            const bool seen = key <= limit_s[row] && key < end && (p.window <= 0 || key > limit_s[row] - p.window);
+            s_s[row * kScoreStride + col] = seen ? c[mt][e] + c_odd[mt][e] : -INFINITY;
           }
       }
       __syncthreads();
@@ -569,7 +588,7 @@ __global__ void __launch_bounds__(128)
 latent_prep_kernel(const float* __restrict__ proj, long long proj_width, int q_off, const int* __restrict__ positions,
                    const float* __restrict__ cos_table, const float* __restrict__ sin_table,
                    __nv_bfloat16* __restrict__ a_heads, float* __restrict__ q_rot, int* __restrict__ tile_group,
-                   int heads, int d, int rot, int padded_tokens, float scale) {
+                   int heads, int d, int rot, int padded_tokens, float scale, int pairing) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -585,10 +604,12 @@ latent_prep_kernel(const float* __restrict__ proj, long long proj_width, int q_o
   const float* sn = sin_table + static_cast<size_t>(position) * (rot / 2);
   for (int i = threadIdx.x; i < heads * (rot / 2); i += blockDim.x) {
     const int h = i / (rot / 2), pair = i % (rot / 2);
-    const float a = row[h * (d + rot) + d + 2 * pair], b = row[h * (d + rot) + d + 2 * pair + 1];
+    int ia, ib;
+    rot_pair(pairing, rot, pair, ia, ib);
+    const float a = row[h * (d + rot) + d + ia], b = row[h * (d + rot) + d + ib];
     float* dst = q_rot + (static_cast<size_t>(t) * heads + h) * rot;
-    dst[2 * pair] = (a * cs[pair] - b * sn[pair]) * scale;
-    dst[2 * pair + 1] = (b * cs[pair] + a * sn[pair]) * scale;
+    dst[ia] = (a * cs[pair] - b * sn[pair]) * scale;
+    dst[ib] = (b * cs[pair] + a * sn[pair]) * scale;
   }
 }
 
@@ -695,6 +716,8 @@ struct LatentParams {
   void* l_heads;           // [heads, padded_tokens, rank]
   float* o_heads;          // [heads, padded_tokens, dv]
   int* tile_group;         // [heads * padded_tokens / 128]
+  int window;              // > 0: a query at position p sees keys p - window + 1 .. p
+  int pairing;             // of the rotated part: 0 values (2i, 2i + 1), 1 values (i, i + rot/2)
 };
 
 // How the tensor-core fold cuts a step: {tokens per tile, heads per tile, keys per split, splits}.
@@ -755,6 +778,7 @@ static int launch_fold_any(const LatentParams& p, cudaStream_t s) {
   f.part = p.part;
   f.num_tokens = p.num_tokens, f.heads = p.heads, f.rank = p.rank, f.rot = p.rot;
   f.table_width = p.table_width, f.page_size = p.page_size;
+  f.window = p.window;
   if (p.stage == 2) {
     f.qa_heads = p.qa_heads, f.q_rot = p.q_rot, f.l_heads = static_cast<__nv_bfloat16*>(p.l_heads);
     f.padded_tokens = p.padded_tokens, f.scale = p.scale;
@@ -799,18 +823,18 @@ static int launch_latent(const LatentParams& p, cudaStream_t s) {
     status = vipera_launch(latent_store_kernel<T>, p.num_tokens, 128, 0, s, p.proj, p.proj_width, p.kv_off, p.norm_weight,
                            p.eps, p.positions, p.cos_table, p.sin_table, static_cast<T*>(p.k_pool),
                            static_cast<T*>(p.v_pool), p.token_entry, p.block_table, p.table_width, p.page_size, p.rank,
-                           p.rot);
+                           p.rot, p.pairing);
     if (status) return status;
   }
   if (p.stage == 1)
     return vipera_launch(latent_prep_kernel, p.num_tokens, 128, 0, s, p.proj, p.proj_width, p.q_off, p.positions, p.cos_table,
                          p.sin_table, static_cast<__nv_bfloat16*>(p.a_heads), p.q_rot, p.tile_group, p.heads, p.d, p.rot,
-                         p.padded_tokens, p.scale);
+                         p.padded_tokens, p.scale, p.pairing);
   const dim3 tiles((p.num_tokens + kTile - 1) / kTile, p.heads);
   const dim3 absorb_grid(tiles.x, tiles.y, (p.rank + 127) / 128);
   status = vipera_launch(latent_absorb_kernel<T>, absorb_grid, 128, kTile * p.d * sizeof(float), s, p.proj, p.proj_width, p.q_off,
                          static_cast<const T*>(p.up_k), p.positions, p.cos_table, p.sin_table, p.qa, p.num_tokens,
-                         p.heads, p.d, p.rank, p.rot, p.scale);
+                         p.heads, p.d, p.rank, p.rot, p.scale, p.pairing);
   if (status) return status;
   // bfloat16 caches whose rows are whole 16-byte pieces fold on the tensor cores
   if (sizeof(T) == 2 && p.rank % 8 == 0 && p.rot % 8 == 0 && p.num_tokens < (1 << 24) / p.heads &&
@@ -820,7 +844,7 @@ static int launch_latent(const LatentParams& p, cudaStream_t s) {
     status = vipera_launch(latent_attention_kernel<T>, dim3(p.num_tokens, (p.heads + kWarps - 1) / kWarps), kWarps * 32,
                            kWarps * (p.rank + p.rot) * sizeof(float), s, p.qa, p.latent_out,
                            static_cast<const T*>(p.k_pool), static_cast<const T*>(p.v_pool), p.token_entry, p.positions,
-                           p.block_table, p.table_width, p.page_size, p.heads, p.rank, p.rot);
+                           p.block_table, p.table_width, p.page_size, p.heads, p.rank, p.rot, p.window);
   if (status) return status;
   const dim3 expand_grid(tiles.x, tiles.y, (p.dv + 31) / 32);
   return vipera_launch(latent_expand_kernel<T, T>, expand_grid, 128, (kTile * p.rank + 4 * kTile * 32) * sizeof(float), s, p.latent_out,
@@ -835,7 +859,7 @@ VIPERA_API int vipera_latent_attention(const LatentParams* params, int dtype, vo
   if (p.rank <= 0 || p.rank > kMaxRank || p.rot <= 0 || p.rot > kMaxRot || (p.rot & 1)) return VIPERA_BAD_SHAPE;
   if (p.heads <= 0 || p.d <= 0 || p.d > 1024 || p.dv <= 0 || p.page_size <= 0 || p.table_width <= 0) return VIPERA_BAD_SHAPE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (p.stage < 0 || p.stage > 3) return VIPERA_BAD_ARGUMENT;
+  if (p.stage < 0 || p.stage > 3 || p.window < 0 || p.pairing < 0 || p.pairing > 1) return VIPERA_BAD_ARGUMENT;
   if (p.stage != 0) {
     if (dtype != VIPERA_BF16 || p.rank % 8 || p.rot % 8 || p.d % 8 || p.padded_tokens < p.num_tokens || p.padded_tokens % 128 ||
         !p.a_heads || !p.qa_heads || !p.q_rot || !p.l_heads || !p.o_heads || !p.tile_group ||

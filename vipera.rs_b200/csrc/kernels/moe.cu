@@ -24,6 +24,15 @@
 //
 // Gate and up matrices are one tensor [experts, 2 ff, hidden]: `gate_group` gate rows, then the
 // up rows of the same features, and so on (16 for the tensor-core ending; ff: all gate rows first).
+//
+// Options.  `gated` = 0: the units have no gate, y_e = D_e act(U_e h), and `gate_up` is [matrices,
+// ff, hidden].  `correction`: a number per router output that is added to the scores for the choice
+// only (the weights are the scores themselves).  `identity`: the last that many router outputs have no
+// matrices; chosen, they return the token's own row times their weight (the router's block writes that
+// row).  `always`: that many units beyond the router's own which every token uses with weight 1 (a
+// shared unit, cut into pieces of the experts' inner size); their matrices follow the chosen experts'
+// in the same tensors, and a token has `slots` = top + always assignments.  With `renormalize` the
+// weights are divided by their sum + `renorm_eps`; `route_scale` multiplies them.
 #include "common.cuh"
 
 constexpr int kTileRows = 32;
@@ -53,7 +62,16 @@ struct MoeParams {
   int gate_group;           // gate rows and up rows alternate in groups of this many
   int tile_rows;            // 8, 32 or (padded) 128
   int padded;               // 1: every expert's run starts at a multiple of tile_rows; capacity = max_tiles * tile_rows
+  const float* correction;  // [experts] added to the scores for the choice; null: nothing
+  int identity;             // the last `identity` of the `experts` router outputs return their input
+  int always;               // units every token uses with weight 1, after the router's own in the matrices
+  int slots;                // top + always: a token's assignments
+  int gated;                // 1: gated units; 0: act(U h)
+  float route_scale, renorm_eps;
 };
+
+// The units that have matrices: the router's outputs without the identity ones, then the ones every token uses.
+__device__ __forceinline__ int moe_matrices(const MoeParams& p) { return p.experts - p.identity + p.always; }
 
 __device__ __forceinline__ size_t gate_row(int feature, int group) {
   return static_cast<size_t>(feature / group) * 2 * group + feature % group;
@@ -112,7 +130,7 @@ moe_route_kernel(MoeParams p) {
     if (lane == 0) score[e] = sum;
   }
   __syncthreads();
-  if (warp != 0) return;
+  if (warp == 0) {
   if (p.softmax_scores) {
     float top_z = -INFINITY;
     for (int e = lane; e < p.experts; e += 32) top_z = fmaxf(top_z, score[e]);
@@ -126,7 +144,10 @@ moe_route_kernel(MoeParams p) {
   }
   __syncwarp();
   // a value that is no number may not win a comparison: it counts as the lowest
-  for (int e = lane; e < p.experts; e += 32) open[e] = score[e] == score[e] ? score[e] : -1.0e30f;
+  for (int e = lane; e < p.experts; e += 32) {
+    const float choice = score[e] + (p.correction ? p.correction[e] : 0.0f);
+    open[e] = choice == choice ? choice : -1.0e30f;
+  }
   __syncwarp();
   const int per_group = p.experts / p.groups;
   if (p.keep < p.groups) {
@@ -177,14 +198,33 @@ moe_route_kernel(MoeParams p) {
     const float w = score[at];
     total += w;
     if (lane == 0) {
-      p.chosen[static_cast<size_t>(t) * p.top + place] = at;
-      p.weight[static_cast<size_t>(t) * p.top + place] = w;
+      // an output without matrices is marked -1 - (its index among those)
+      p.chosen[static_cast<size_t>(t) * p.slots + place] = at < p.experts - p.identity ? at : -1 - (at - (p.experts - p.identity));
+      p.weight[static_cast<size_t>(t) * p.slots + place] = w;
       open[at] = -INFINITY;
     }
     __syncwarp();
   }
-  if (p.renormalize && lane == 0)
-    for (int place = 0; place < p.top; ++place) p.weight[static_cast<size_t>(t) * p.top + place] /= total;
+  if (lane == 0) {
+    const float divisor = p.renormalize ? total + p.renorm_eps : 1.0f;
+    for (int place = 0; place < p.top; ++place) {
+      const size_t a = static_cast<size_t>(t) * p.slots + place;
+      p.weight[a] = p.weight[a] / divisor * p.route_scale;
+    }
+    for (int extra = 0; extra < p.always; ++extra) {
+      p.chosen[static_cast<size_t>(t) * p.slots + p.top + extra] = p.experts - p.identity + extra;
+      p.weight[static_cast<size_t>(t) * p.slots + p.top + extra] = 1.0f;
+    }
+  }
+  }
+  if (p.identity == 0) return;
+  __syncthreads();   // the choice is written
+  for (int place = 0; place < p.top; ++place) {
+    const size_t a = static_cast<size_t>(t) * p.slots + place;
+    if (p.chosen[a] >= 0) continue;
+    const float w = p.weight[a];
+    for (int i = threadIdx.x; i < p.hidden; i += kRouteThreads) p.rows[a * p.hidden + i] = w * h_s[i];
+  }
 }
 
 // One block: assignments counted per expert, the experts' runs cut into tiles, the sorted order.
@@ -194,17 +234,19 @@ moe_group_kernel(MoeParams p) {
   __shared__ int start[kMaxExperts];
   pdl_launch_dependents();
   pdl_wait();
-  const int assignments = p.num_tokens * p.top;
-  for (int e = threadIdx.x; e < p.experts; e += blockDim.x) count[e] = 0;
+  const int assignments = p.num_tokens * p.slots;
+  const int matrices = moe_matrices(p);
+  for (int e = threadIdx.x; e < matrices; e += blockDim.x) count[e] = 0;
   for (int tile = threadIdx.x; tile < p.max_tiles; tile += blockDim.x) p.tile_expert[tile] = 0;
   if (p.padded)
     for (int place = threadIdx.x; place < p.max_tiles * p.tile_rows; place += blockDim.x) p.order[place] = -1;
   __syncthreads();
-  for (int a = threadIdx.x; a < assignments; a += blockDim.x) p.rank[a] = atomicAdd(&count[p.chosen[a]], 1);
+  for (int a = threadIdx.x; a < assignments; a += blockDim.x)
+    p.rank[a] = p.chosen[a] >= 0 ? atomicAdd(&count[p.chosen[a]], 1) : -1;   // (-1: no matrices, no place)
   __syncthreads();
   if (threadIdx.x == 0) {
     int place = 0, tile = 0;
-    for (int e = 0; e < p.experts; ++e) {
+    for (int e = 0; e < matrices; ++e) {
       start[e] = place;
       int first = 0;
       for (; first < count[e] && tile < p.max_tiles; first += p.tile_rows, ++tile) {
@@ -219,6 +261,7 @@ moe_group_kernel(MoeParams p) {
   }
   __syncthreads();
   for (int a = threadIdx.x; a < assignments; a += blockDim.x) {
+    if (p.chosen[a] < 0) continue;
     const int place = start[p.chosen[a]] + p.rank[a];
     p.rank[a] = place;
     p.order[place] = a;
@@ -240,7 +283,7 @@ moe_gather_kernel(MoeParams p) {
     for (int i = threadIdx.x; i < vectors; i += blockDim.x) dst[i] = make_uint4(0u, 0u, 0u, 0u);
     return;
   }
-  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(p.h) + static_cast<size_t>(a / p.top) * p.hidden);
+  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(p.h) + static_cast<size_t>(a / p.slots) * p.hidden);
   for (int i = threadIdx.x; i < vectors; i += blockDim.x) dst[i] = src[i];
 }
 
@@ -251,8 +294,9 @@ moe_scatter_kernel(MoeParams p) {
   pdl_wait();
   const int quarter = p.hidden / 4;
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= static_cast<long long>(p.num_tokens) * p.top * quarter) return;
+  if (i >= static_cast<long long>(p.num_tokens) * p.slots * quarter) return;
   const int a = static_cast<int>(i / quarter), c = static_cast<int>(i % quarter);
+  if (p.rank[a] < 0) return;   // the router's block wrote this row
   const float w = p.weight[a];
   float4 v = reinterpret_cast<const float4*>(p.ys + static_cast<size_t>(p.rank[a]) * p.hidden)[c];
   v.x *= w, v.y *= w, v.z *= w, v.w *= w;
@@ -289,9 +333,12 @@ __device__ __forceinline__ void load_span<__nv_bfloat16, 1>(const __nv_bfloat16*
   dst[0] = __bfloat162float(src[0]);
 }
 
-template <typename T, bool GATED, int VEC>
+// MODE 0: the down product; 1: gate and up with the gated unit as ending; 2: up alone with its activation.
+template <typename T, int MODE, int VEC>
 __global__ void __launch_bounds__(256)
 moe_skinny_kernel(MoeParams p) {
+  constexpr bool GATED = MODE == 1;
+  constexpr bool FIRST = MODE != 0;
   extern __shared__ __align__(16) unsigned char skinny_shared[];
   T* x_s = reinterpret_cast<T*>(skinny_shared);   // [kSkinnyRows][inner]
   pdl_launch_dependents();
@@ -299,12 +346,12 @@ moe_skinny_kernel(MoeParams p) {
   const int tile = blockIdx.y;
   if (tile >= p.tiles[0]) return;
   const int expert = p.tiles[1 + 3 * tile], first = p.tiles[2 + 3 * tile], rows = p.tiles[3 + 3 * tile];
-  const int inner = GATED ? p.hidden : p.ff;
-  const int outer = GATED ? p.ff : p.hidden;
-  const T* x = static_cast<const T*>(GATED ? p.h : p.act);
+  const int inner = FIRST ? p.hidden : p.ff;
+  const int outer = FIRST ? p.ff : p.hidden;
+  const T* x = static_cast<const T*>(FIRST ? p.h : p.act);
   for (int i = threadIdx.x * VEC; i < rows * inner; i += 256 * VEC) {
     const int r = i / inner, k = i % inner;   // (inner is a multiple of VEC)
-    const size_t source = GATED ? static_cast<size_t>(p.order[first + r] / p.top) : static_cast<size_t>(first + r);
+    const size_t source = FIRST ? static_cast<size_t>(p.order[first + r] / p.slots) : static_cast<size_t>(first + r);
     if (VEC > 1) *reinterpret_cast<uint4*>(x_s + i) = *reinterpret_cast<const uint4*>(x + source * inner + k);
     else x_s[i] = x[source * inner + k];
   }
@@ -315,7 +362,7 @@ moe_skinny_kernel(MoeParams p) {
   const int col0 = (blockIdx.x * 8 + warp) * per_warp;
   if (col0 >= outer) return;
   const T* w_rows[4];
-  const T* base = static_cast<const T*>(GATED ? p.gate_up : p.down) +
+  const T* base = static_cast<const T*>(FIRST ? p.gate_up : p.down) +
                   static_cast<size_t>(expert) * (GATED ? 2 : 1) * outer * inner;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -359,6 +406,11 @@ moe_skinny_kernel(MoeParams p) {
         if (col0 + f < outer)
           static_cast<T*>(p.act)[static_cast<size_t>(first + r) * p.ff + col0 + f] =
               from_float<T>(gate_activation(acc[2 * f][r], p.activation) * acc[2 * f + 1][r]);
+    } else if (FIRST) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (col0 + j < outer)
+          static_cast<T*>(p.act)[static_cast<size_t>(first + r) * p.ff + col0 + j] = from_float<T>(gate_activation(acc[j][r], p.activation));
     } else {
       const int a = p.order[first + r];
       const float weight = p.weight[a];
@@ -375,9 +427,11 @@ moe_skinny_kernel(MoeParams p) {
 // else:  rows[a, :] = w_a * (D_e act[sorted place of a]).
 // Threads: 16 across the columns (columns c, c + 16, c + 32, c + 48) by 16 down the rows (r, r + 16).
 // ---------------------------------------------------------------------------------------
-template <typename T, bool GATED>
+template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_product_kernel(MoeParams p) {
+  constexpr bool GATED = MODE == 1;
+  constexpr bool FIRST = MODE != 0;
   __shared__ float x_s[kTileRows][kTileInner + 1];
   __shared__ float w_s[GATED ? 2 : 1][kTileCols][kTileInner + 1];
   __shared__ int row_source[kTileRows];
@@ -386,18 +440,18 @@ moe_product_kernel(MoeParams p) {
   const int tile = blockIdx.y;
   if (tile >= p.tiles[0]) return;
   const int expert = p.tiles[1 + 3 * tile], first = p.tiles[2 + 3 * tile], rows = p.tiles[3 + 3 * tile];
-  const int inner = GATED ? p.hidden : p.ff;
-  const int outer = GATED ? p.ff : p.hidden;
+  const int inner = FIRST ? p.hidden : p.ff;
+  const int outer = FIRST ? p.ff : p.hidden;
   const int col0 = blockIdx.x * kTileCols;
   if (threadIdx.x < kTileRows) {
     int source = -1;
-    if (threadIdx.x < rows) source = GATED ? p.order[first + threadIdx.x] / p.top : first + threadIdx.x;
+    if (threadIdx.x < rows) source = FIRST ? p.order[first + threadIdx.x] / p.slots : first + threadIdx.x;
     row_source[threadIdx.x] = source;
   }
   __syncthreads();
-  const T* x = static_cast<const T*>(GATED ? p.h : p.act);
+  const T* x = static_cast<const T*>(FIRST ? p.h : p.act);
   // GATED: the gate row of feature c is at gate_row(c), its up row gate_group rows further
-  const T* w0 = static_cast<const T*>(GATED ? p.gate_up : p.down) + static_cast<size_t>(expert) * (GATED ? 2 : 1) * outer * inner;
+  const T* w0 = static_cast<const T*>(FIRST ? p.gate_up : p.down) + static_cast<size_t>(expert) * (GATED ? 2 : 1) * outer * inner;
   const T* w1 = GATED ? w0 + static_cast<size_t>(p.gate_group) * inner : nullptr;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float acc0[2][4], acc1[2][4];
@@ -447,6 +501,8 @@ moe_product_kernel(MoeParams p) {
       if (GATED) {
         static_cast<T*>(p.act)[static_cast<size_t>(first + r) * p.ff + c] =
             from_float<T>(gate_activation(acc0[i][j], p.activation) * acc1[i][j]);
+      } else if (FIRST) {
+        static_cast<T*>(p.act)[static_cast<size_t>(first + r) * p.ff + c] = from_float<T>(gate_activation(acc0[i][j], p.activation));
       } else {
         const int a = p.order[first + r];
         p.rows[static_cast<size_t>(a) * p.hidden + c] = p.weight[a] * acc0[i][j];
@@ -455,31 +511,33 @@ moe_product_kernel(MoeParams p) {
   }
 }
 
-template <typename T, bool GATED>
+template <typename T, int MODE>
 static int launch_skinny(const MoeParams& p, cudaStream_t s) {
   constexpr int kVec = 16 / static_cast<int>(sizeof(T));
-  const int inner = GATED ? p.hidden : p.ff;
-  const int outer = GATED ? p.ff : p.hidden;
-  const uintptr_t bases = reinterpret_cast<uintptr_t>(GATED ? p.h : p.act) | reinterpret_cast<uintptr_t>(GATED ? p.gate_up : p.down);
+  constexpr bool GATED = MODE == 1;
+  constexpr bool FIRST = MODE != 0;
+  const int inner = FIRST ? p.hidden : p.ff;
+  const int outer = FIRST ? p.ff : p.hidden;
+  const uintptr_t bases = reinterpret_cast<uintptr_t>(FIRST ? p.h : p.act) | reinterpret_cast<uintptr_t>(FIRST ? p.gate_up : p.down);
   const bool whole = inner % kVec == 0 && (bases & 15) == 0;
   const size_t shared = static_cast<size_t>(kSkinnyRows) * inner * sizeof(T);
   const dim3 grid((outer + (GATED ? 16 : 32) - 1) / (GATED ? 16 : 32), p.max_tiles);
   if (whole) {
     static bool configured = false;
     if (!configured) {
-      if (cudaFuncSetAttribute(moe_skinny_kernel<T, GATED, kVec>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+      if (cudaFuncSetAttribute(moe_skinny_kernel<T, MODE, kVec>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
         return VIPERA_BAD_ARGUMENT;
       configured = true;
     }
-    return vipera_launch(moe_skinny_kernel<T, GATED, kVec>, grid, 256, shared, s, p);
+    return vipera_launch(moe_skinny_kernel<T, MODE, kVec>, grid, 256, shared, s, p);
   }
   static bool configured_single = false;
   if (!configured_single) {
-    if (cudaFuncSetAttribute(moe_skinny_kernel<T, GATED, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+    if (cudaFuncSetAttribute(moe_skinny_kernel<T, MODE, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
       return VIPERA_BAD_ARGUMENT;
     configured_single = true;
   }
-  return vipera_launch(moe_skinny_kernel<T, GATED, 1>, grid, 256, shared, s, p);
+  return vipera_launch(moe_skinny_kernel<T, MODE, 1>, grid, 256, shared, s, p);
 }
 
 // The router, the grouping and (padded form) the gathered rows.
@@ -502,12 +560,14 @@ static int launch_route(const MoeParams& p, cudaStream_t s) {
 template <typename T>
 static int launch_products(const MoeParams& p, cudaStream_t s) {
   if (p.tile_rows == kSkinnyRows) {
-    const int status = launch_skinny<T, true>(p, s);
-    return status ? status : launch_skinny<T, false>(p, s);
+    const int status = p.gated ? launch_skinny<T, 1>(p, s) : launch_skinny<T, 2>(p, s);
+    return status ? status : launch_skinny<T, 0>(p, s);
   }
-  int status = vipera_launch(moe_product_kernel<T, true>, dim3((p.ff + kTileCols - 1) / kTileCols, p.max_tiles), 256, 0, s, p);
+  const dim3 first_grid((p.ff + kTileCols - 1) / kTileCols, p.max_tiles);
+  int status = p.gated ? vipera_launch(moe_product_kernel<T, 1>, first_grid, 256, 0, s, p)
+                       : vipera_launch(moe_product_kernel<T, 2>, first_grid, 256, 0, s, p);
   if (status) return status;
-  return vipera_launch(moe_product_kernel<T, false>, dim3((p.hidden + kTileCols - 1) / kTileCols, p.max_tiles), 256, 0, s, p);
+  return vipera_launch(moe_product_kernel<T, 0>, dim3((p.hidden + kTileCols - 1) / kTileCols, p.max_tiles), 256, 0, s, p);
 }
 
 static int check_moe(const MoeParams& p) {
@@ -515,8 +575,12 @@ static int check_moe(const MoeParams& p) {
       p.keep > p.groups || p.top <= 0 || p.top > p.keep * (p.experts / p.groups) || p.group_top < 1 || p.group_top > 2 ||
       p.hidden <= 0 || p.ff <= 0 || p.gate_group <= 0 || p.ff % p.gate_group)
     return VIPERA_BAD_SHAPE;
+  if (p.identity < 0 || p.identity > p.experts || p.always < 0 || p.slots != p.top + p.always ||
+      p.experts - p.identity + p.always > kMaxExperts || (p.identity > 0 && !p.rows))
+    return VIPERA_BAD_SHAPE;
   if (p.padded ? p.tile_rows != 128 : (p.tile_rows != kSkinnyRows && p.tile_rows != kTileRows)) return VIPERA_BAD_ARGUMENT;
-  if (p.max_tiles < p.num_tokens * p.top / p.tile_rows + min(p.experts, p.num_tokens * p.top) || p.max_tiles > 65535)
+  if (p.max_tiles < p.num_tokens * p.slots / p.tile_rows + min(p.experts - p.identity + p.always, p.num_tokens * p.slots) ||
+      p.max_tiles > 65535)
     return VIPERA_BAD_ARGUMENT;
   if (static_cast<size_t>(2 * p.experts + p.groups + p.hidden) * sizeof(float) > 200 * 1024) return VIPERA_BAD_SHAPE;
   if (p.tile_rows == kSkinnyRows && static_cast<size_t>(kSkinnyRows) * max(p.hidden, p.ff) * 4 > 200 * 1024) return VIPERA_BAD_SHAPE;
@@ -550,7 +614,7 @@ VIPERA_API int vipera_moe_scatter(const MoeParams* params, void* stream) {
   const MoeParams& p = *params;
   if (p.num_tokens <= 0) return VIPERA_OK;
   if (!p.padded || p.hidden % 4) return VIPERA_BAD_ARGUMENT;
-  const long long count = static_cast<long long>(p.num_tokens) * p.top * (p.hidden / 4);
+  const long long count = static_cast<long long>(p.num_tokens) * p.slots * (p.hidden / 4);
   return vipera_launch(moe_scatter_kernel, static_cast<unsigned>((count + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream), p);
 }
 

@@ -108,13 +108,15 @@ rope_cache_partial_kernel(const float* __restrict__ qkv, T* __restrict__ q_out, 
                           int head_dim, int value_dim, int rot_dims, const int* __restrict__ positions,
                           const float* __restrict__ cos_table, const float* __restrict__ sin_table, int style,
                           T* __restrict__ k_pool, T* __restrict__ v_pool, const int* __restrict__ token_seq,
-                          const int* __restrict__ block_table, int table_width, int page_size, int write_cache) {
+                          const int* __restrict__ block_table, int table_width, int page_size, int write_cache,
+                          long long row_stride, float* __restrict__ v_publish, const float* __restrict__ v_blend,
+                          const float* __restrict__ blend) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   const int qk_width = (num_heads + num_kv_heads) * head_dim;
   const int v_width = num_kv_heads * value_dim;
-  const float* row = qkv + static_cast<size_t>(t) * (qk_width + v_width);
+  const float* row = qkv + static_cast<size_t>(t) * row_stride;
   const int position = positions[t];
   T* k_row = nullptr;
   T* v_row = nullptr;
@@ -147,8 +149,54 @@ rope_cache_partial_kernel(const float* __restrict__ qkv, T* __restrict__ q_out, 
     if (h < num_heads) q_out[(static_cast<size_t>(t) * num_heads + h) * head_dim + e] = from_float<T>(value);
     else if (k_row) k_row[static_cast<size_t>(h - num_heads) * head_dim + e] = from_float<T>(value);
   }
-  if (v_row)
-    for (int item = threadIdx.x; item < v_width; item += blockDim.x) v_row[item] = from_float<T>(row[qk_width + item]);
+  // Values: as projected, or blended with the values another layer published for the same tokens,
+  // v = (1 - b) v + b v_other with b = blend[0], in 32-bit; `v_publish` receives this layer's values
+  // as projected (32-bit), for the layers behind it.
+  if (v_publish)
+    for (int item = threadIdx.x; item < v_width; item += blockDim.x)
+      v_publish[static_cast<size_t>(t) * v_width + item] = row[qk_width + item];
+  if (v_row) {
+    const float b = v_blend ? blend[0] : 0.0f;
+    for (int item = threadIdx.x; item < v_width; item += blockDim.x) {
+      float value = row[qk_width + item];
+      if (v_blend) value = (1.0f - b) * value + b * v_blend[static_cast<size_t>(t) * v_width + item];
+      v_row[item] = from_float<T>(value);
+    }
+  }
+}
+
+// The general form with the input's rows `row_stride` floats apart (q, k, v first; what follows them
+// is not read) and values that are published or blended: `v_publish` (null: not) receives the values
+// as projected, 32-bit [tokens, kv_heads * value_dim]; with `v_blend` (null: not) the cached values
+// are (1 - blend[0]) v + blend[0] v_blend, `blend` a 32-bit number on the device.
+VIPERA_API int vipera_rope_cache_blend(const float* qkv, long long row_stride, void* q_out, int dtype, int num_tokens,
+                                       int num_heads, int num_kv_heads, int head_dim, int value_dim, int rot_dims,
+                                       const int* positions, const float* cos_table, const float* sin_table, int style,
+                                       void* k_pool, void* v_pool, const int* token_seq, const int* block_table,
+                                       int table_width, int page_size, int write_cache, float* v_publish,
+                                       const float* v_blend, const float* blend, void* stream) {
+  if (num_tokens <= 0) return VIPERA_OK;
+  if (head_dim <= 0 || value_dim <= 0 || num_heads <= 0 || num_kv_heads <= 0) return VIPERA_BAD_SHAPE;
+  if (rot_dims < 0 || (rot_dims & 1) || rot_dims > head_dim) return VIPERA_BAD_SHAPE;
+  if (row_stride < static_cast<long long>(num_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim) return VIPERA_BAD_SHAPE;
+  if (style != ROPE_NONE && rot_dims > 0 && (!cos_table || !sin_table)) return VIPERA_BAD_ARGUMENT;
+  if (write_cache && (!k_pool || !v_pool || !token_seq || !block_table || page_size <= 0)) return VIPERA_BAD_ARGUMENT;
+  if (v_blend && !blend) return VIPERA_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  dim3 grid(num_tokens);
+  const int work = (num_heads + num_kv_heads) * head_dim;
+  const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+  if (dtype == VIPERA_F32)
+    return vipera_launch(rope_cache_partial_kernel<float>, grid, threads, 0, s, qkv, static_cast<float*>(q_out), num_heads,
+        num_kv_heads, head_dim, value_dim, rot_dims, positions, cos_table, sin_table, style, static_cast<float*>(k_pool),
+        static_cast<float*>(v_pool), token_seq, block_table, table_width, page_size, write_cache, row_stride, v_publish,
+        v_blend, blend);
+  if (dtype == VIPERA_BF16)
+    return vipera_launch(rope_cache_partial_kernel<__nv_bfloat16>, grid, threads, 0, s, qkv, static_cast<__nv_bfloat16*>(q_out),
+        num_heads, num_kv_heads, head_dim, value_dim, rot_dims, positions, cos_table, sin_table, style,
+        static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool), token_seq, block_table, table_width,
+        page_size, write_cache, row_stride, v_publish, v_blend, blend);
+  return VIPERA_BAD_DTYPE;
 }
 
 VIPERA_API int vipera_rope_cache_partial(const float* qkv, void* q_out, int dtype, int num_tokens, int num_heads,
@@ -164,17 +212,19 @@ VIPERA_API int vipera_rope_cache_partial(const float* qkv, void* q_out, int dtyp
   if (write_cache && (!k_pool || !v_pool || !token_seq || !block_table || page_size <= 0)) return VIPERA_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   dim3 grid(num_tokens);
+  const long long stride = static_cast<long long>(num_heads + num_kv_heads) * head_dim + static_cast<long long>(num_kv_heads) * value_dim;
   const int work = (num_heads + num_kv_heads) * head_dim;
   const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
   if (dtype == VIPERA_F32)
     return vipera_launch(rope_cache_partial_kernel<float>, grid, threads, 0, s, qkv, static_cast<float*>(q_out), num_heads,
         num_kv_heads, head_dim, value_dim, rot_dims, positions, cos_table, sin_table, style, static_cast<float*>(k_pool),
-        static_cast<float*>(v_pool), token_seq, block_table, table_width, page_size, write_cache);
+        static_cast<float*>(v_pool), token_seq, block_table, table_width, page_size, write_cache, stride, nullptr, nullptr,
+        nullptr);
   if (dtype == VIPERA_BF16)
     return vipera_launch(rope_cache_partial_kernel<__nv_bfloat16>, grid, threads, 0, s, qkv, static_cast<__nv_bfloat16*>(q_out),
         num_heads, num_kv_heads, head_dim, value_dim, rot_dims, positions, cos_table, sin_table, style,
         static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool), token_seq, block_table, table_width,
-        page_size, write_cache);
+        page_size, write_cache, stride, nullptr, nullptr, nullptr);
   return VIPERA_BAD_DTYPE;
 }
 

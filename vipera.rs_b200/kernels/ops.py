@@ -20,8 +20,9 @@ from ..errors import InternalError, InvalidArgumentError, UnsupportedError
 F32, BF16 = 0, 1
 EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
 EPI_GATED = EPI_SWIGLU   # the gated unit over interleaved gate and up rows; its activation is an argument
-ACT_SILU, ACT_GELU_TANH = 0, 1
-ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
+ACT_SILU, ACT_GELU_TANH, ACT_RELU2 = 0, 1, 2
+ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}   # of a gated unit's gate
+UNIT_ACTIVATIONS = {**ACTIVATIONS, "relu2": ACT_RELU2}          # of a unit without a gate (relu2: the square of relu)
 ROPE_NONE, ROPE_NEOX, ROPE_INTERLEAVED = 0, 1, 2
 SAMPLE_OK, SAMPLE_NO_FINITE, SAMPLE_NO_MASS, SAMPLE_NEEDS_HOST = 0, 1, 2, 3
 
@@ -307,6 +308,50 @@ def _rope_cache_partial(qkv, q_out, *, num_heads, num_kv_heads, head_dim, value_
               _stream()), "rope_cache")
 
 
+def rope_cache_blend(qkv: torch.Tensor, q_out: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int,
+                     value_dim: int, rot_dims: int, positions: torch.Tensor, cos: Optional[torch.Tensor],
+                     sin: Optional[torch.Tensor], style: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                     token_seq: torch.Tensor, block_table: torch.Tensor, page_size: int, write_cache: bool,
+                     publish: Optional[torch.Tensor] = None, blend_with: Optional[torch.Tensor] = None,
+                     blend: Optional[torch.Tensor] = None) -> None:
+    """The general rotation and cache write over a float32 product whose rows may hold more than
+    q, k and v (the rest is not read), with values that are published or blended: ``publish``
+    float32 [tokens, kv_heads * value_dim] receives the values as projected; with ``blend_with`` (the
+    same shape) the cached values are ``(1 - b) v + b blend_with``, b the 32-bit number ``blend``."""
+    fn = _function("rope_cache", "vipera_rope_cache_blend",
+                   [_c_void, ctypes.c_longlong, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void,
+                    _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void, _c_void,
+                    _c_void, _c_void])
+    count = qkv.shape[0]
+    v_width = num_kv_heads * value_dim
+    if qkv.dim() != 2 or qkv.stride(1) != 1 or qkv.shape[1] < (num_heads + num_kv_heads) * head_dim + v_width:
+        raise InvalidArgumentError("rope_cache: qkv rows are too short for the head counts and sizes")
+    if q_out.shape[0] != count or q_out.shape[1] != num_heads * head_dim:
+        raise InvalidArgumentError("rope_cache: q_out has the wrong shape")
+    if rot_dims % 2 or not 0 <= rot_dims <= head_dim:
+        raise InvalidArgumentError("rope_cache: the rotated values must be an even count within the head")
+    if style != ROPE_NONE and rot_dims:
+        if cos is None or sin is None or cos.shape[1] != rot_dims // 2 or sin.shape != cos.shape:
+            raise InvalidArgumentError("rope_cache: cos/sin tables of width rot_dims/2 are needed")
+    if write_cache and (k_pool.dtype != q_out.dtype or v_pool.dtype != q_out.dtype or
+                        k_pool.shape[1:] != (page_size, num_kv_heads, head_dim) or
+                        v_pool.shape[1:] != (page_size, num_kv_heads, value_dim)):
+        raise InvalidArgumentError("rope_cache: cache pools must be [pages, page_size, kv_heads, d] and "
+                                   "[pages, page_size, kv_heads, value size] of the activation dtype")
+    for other in (publish, blend_with):
+        if other is not None and (tuple(other.shape) != (count, v_width) or not other.is_contiguous()):
+            raise InvalidArgumentError("rope_cache: published and blended values are [tokens, kv_heads * value size]")
+    if blend_with is not None and (blend is None or blend.numel() != 1):
+        raise InvalidArgumentError("rope_cache: blending needs one 32-bit number")
+    _check(fn(_gpu(qkv, "qkv", torch.float32), int(qkv.stride(0)), _gpu(q_out, "q_out"), dtype_code(q_out.dtype), count,
+              num_heads, num_kv_heads, head_dim, value_dim, rot_dims, _gpu(positions, "positions", torch.int32),
+              _opt(cos, "cos", torch.float32), _opt(sin, "sin", torch.float32), style, _gpu(k_pool, "k_pool"),
+              _gpu(v_pool, "v_pool"), _gpu(token_seq, "token_seq", torch.int32),
+              _gpu(block_table, "block_table", torch.int32), block_table.shape[1], page_size, 1 if write_cache else 0,
+              _opt(publish, "publish", torch.float32), _opt(blend_with, "blend_with", torch.float32),
+              _opt(blend, "blend", torch.float32), _stream()), "rope_cache")
+
+
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_STORE,
               bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
               resid: Optional[torch.Tensor] = None, activation: int = ACT_SILU) -> None:
@@ -349,15 +394,20 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: 
               token_seq: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
               num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
               value_dim: Optional[int] = None, keep_first: int = 0, sink: bool = False, chunk: int = 0,
-              out_scale: float = 1.0) -> None:
+              out_scale: float = 1.0, sink_values: Optional[torch.Tensor] = None,
+              gate: Optional[torch.Tensor] = None, gate_offset: int = 0) -> None:
     """Causal grouped-query attention of every token of the step over its request's pages.
     ``value_dim``: a value row's size (default d); ``keep_first``: with a window, that many
     first keys stay visible; ``sink``: one is added to the softmax's denominator; ``chunk``:
     instead of a window, a query sees the earlier keys of its own chunk of that many positions
-    (chunks counted from position 0); ``out_scale`` multiplies the output."""
-    fn = _function("attention", "vipera_attention",
+    (chunks counted from position 0); ``out_scale`` multiplies the output.  ``sink_values``
+    float32 [heads]: exp(sink_h) joins head h's denominator instead of one.  ``gate`` float32
+    [tokens, width]: the output is multiplied by the sigmoid of the heads * value_dim values that
+    start at column ``gate_offset`` of the token's row."""
+    fn = _function("attention", "vipera_attention_gated",
                    [_c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int,
-                    _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void])
+                    _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void,
+                    _c_void, ctypes.c_longlong, _c_void])
     if chunk and window:
         raise InvalidArgumentError("attention: a mask is a window or chunks, not both")
     count = q.shape[0]
@@ -373,12 +423,21 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     if k_pool.shape[2:] != (num_kv_heads, head_dim) or v_pool.shape[3] != value_dim:
         raise InvalidArgumentError("attention: cache pools must be [pages, page_size, kv_heads, d] and "
                                    "[pages, page_size, kv_heads, value size]")
+    if sink_values is not None and sink_values.numel() != num_heads:
+        raise InvalidArgumentError("attention: one sink score per query head")
+    gate_pointer, gate_stride = None, 0
+    if gate is not None:
+        if gate.dim() != 2 or gate.shape[0] != count or gate.stride(1) != 1 or \
+                not 0 <= gate_offset <= gate.shape[1] - num_heads * value_dim:
+            raise InvalidArgumentError("attention: the gate must hold heads * value size values per token")
+        gate_pointer = _gpu(gate, "gate", torch.float32) + 4 * int(gate_offset)
+        gate_stride = int(gate.stride(0))
     _check(fn(_gpu(q, "q"), _gpu(out, "out"), dtype_code(q.dtype), _gpu(k_pool, "k_pool"), _gpu(v_pool, "v_pool"),
               _gpu(token_seq, "token_seq", torch.int32), _gpu(positions, "positions", torch.int32),
               _gpu(block_table, "block_table", torch.int32), block_table.shape[1], page_size, count,
               num_heads, num_kv_heads, head_dim, value_dim, float(scale), int(window or 0),
               int(keep_first or 0) if window else 0, 1 if sink else 0, int(chunk or 0), float(out_scale),
-              _stream()), "attention")
+              _opt(sink_values, "sink_values", torch.float32), gate_pointer, gate_stride, _stream()), "attention")
 
 
 # ----------------------------------------------------------------------------------------
@@ -1436,6 +1495,7 @@ class _LatentParams(ctypes.Structure):
         ("part", _c_void), ("split_keys", _c_int), ("num_splits", _c_int),
         ("stage", _c_int), ("padded_tokens", _c_int), ("a_heads", _c_void), ("qa_heads", _c_void), ("q_rot", _c_void),
         ("l_heads", _c_void), ("o_heads", _c_void), ("tile_group", _c_void),
+        ("window", _c_int), ("pairing", _c_int),
     ]
 
 
@@ -1460,7 +1520,8 @@ def latent_attention(proj: torch.Tensor, *, q_off: int, g_off: int, kv_off: int,
                      block_table: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, k_pool: torch.Tensor,
                      v_pool: torch.Tensor, qa: torch.Tensor, latent_out: torch.Tensor, out: torch.Tensor, heads: int,
                      head_dim: int, rot_dim: int, value_dim: int, scale: float, max_keys: int = 0,
-                     part: Optional[torch.Tensor] = None, head_major: Optional[dict] = None) -> None:
+                     part: Optional[torch.Tensor] = None, head_major: Optional[dict] = None, window: int = 0,
+                     pairing: int = ROPE_INTERLEAVED) -> None:
     """Causal softmax attention whose keys and values are products of a cached latent.  ``proj``
     float32 [tokens, width] holds q (head by head [head_dim | rot_dim]) at column ``q_off``, the
     output gate's pre-activation at ``g_off`` (negative: no gate) and the down projection
@@ -1477,7 +1538,9 @@ def latent_attention(proj: torch.Tensor, *, q_off: int, g_off: int, kv_off: int,
     ``up_v_rows`` [heads, value_dim, rank] and the scratch ``a_heads`` (bfloat16 [heads * padded,
     head_dim]), ``qa_heads`` (float32 [heads * padded, rank]), ``q_rot`` (float32 [tokens, heads *
     rot_dim]), ``l_heads`` (bfloat16 [heads * padded, rank]), ``o_heads`` (float32 [heads * padded,
-    value_dim]) and ``tile_group`` (int32 [heads * padded / 128])."""
+    value_dim]) and ``tile_group`` (int32 [heads * padded / 128]).  ``window`` > 0: a query at position
+    p sees keys p - window + 1 .. p.  ``pairing``: which values of the rotated part turn together,
+    ROPE_INTERLEAVED (2i, 2i + 1) or ROPE_NEOX (i, i + rot_dim / 2)."""
     fn = _function("latent", "vipera_latent_attention", [ctypes.POINTER(_LatentParams), _c_int, _c_void])
     _check_struct("latent", "vipera_latent_params_size", _LatentParams)
     tokens = proj.shape[0]
@@ -1511,6 +1574,9 @@ def latent_attention(proj: torch.Tensor, *, q_off: int, g_off: int, kv_off: int,
     p.num_tokens, p.heads, p.d, p.rot, p.dv, p.rank = int(tokens), int(heads), int(head_dim), int(rot_dim), int(value_dim), int(rank)
     p.table_width, p.page_size = int(block_table.shape[1]), int(page_size)
     p.scale, p.eps = float(scale), float(eps)
+    if pairing not in (ROPE_INTERLEAVED, ROPE_NEOX):
+        raise InvalidArgumentError("latent_attention: the rotated part turns as interleaved pairs or as halves")
+    p.window, p.pairing = int(window or 0), 1 if pairing == ROPE_NEOX else 0
     p.part, p.split_keys, p.num_splits = None, 0, 1
     if part is not None and max_keys > 0:
         _, _, split_keys, splits = latent_plan(tokens, heads, int(max_keys), sm_count(proj.device))
@@ -1611,6 +1677,8 @@ class _MoeParams(ctypes.Structure):
         ("groups", _c_int), ("keep", _c_int), ("group_top", _c_int), ("max_tiles", _c_int),
         ("softmax_scores", _c_int), ("renormalize", _c_int), ("activation", _c_int),
         ("gate_group", _c_int), ("tile_rows", _c_int), ("padded", _c_int),
+        ("correction", _c_void), ("identity", _c_int), ("always", _c_int), ("slots", _c_int), ("gated", _c_int),
+        ("route_scale", _c_float), ("renorm_eps", _c_float),
     ]
 
 
@@ -1667,7 +1735,9 @@ def gemm_tc_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, 
 def moe(h: torch.Tensor, *, router: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, gate_group: int, top: int,
         groups: int, keep: int, group_top: int, softmax_scores: bool, renormalize: bool, activation: int,
         chosen: torch.Tensor, weight: torch.Tensor, scratch: torch.Tensor, act: torch.Tensor, rows: torch.Tensor,
-        xs: Optional[torch.Tensor] = None, ys: Optional[torch.Tensor] = None) -> None:
+        xs: Optional[torch.Tensor] = None, ys: Optional[torch.Tensor] = None, gated: bool = True,
+        correction: Optional[torch.Tensor] = None, identity: int = 0, always: int = 0, route_scale: float = 1.0,
+        renorm_eps: float = 0.0) -> None:
     """A mixture of gated units over a step.  ``h`` [tokens, hidden]; ``router`` float32 [experts,
     hidden]; ``gate_up`` [experts, 2 ff, hidden] (``gate_group`` gate rows, then the up rows of the
     same features, and so on) and ``down`` [experts, hidden, ff] in h's type.  ``chosen`` int32 and
@@ -1675,17 +1745,32 @@ def moe(h: torch.Tensor, *, router: torch.Tensor, gate_up: torch.Tensor, down: t
     float32 [tokens, top, hidden] receives each chosen expert's weighted output (their sum over
     ``top`` is the mixture's output).  ``scratch`` int32 of moe_scratch_words(...) words; ``act``
     [moe_capacity(...), ff] in h's type; ``xs`` (h's type) and ``ys`` (float32) [moe_capacity(...),
-    hidden] for the form that runs on the tensor cores."""
+    hidden] for the form that runs on the tensor cores.
+
+    ``gated`` false: units without a gate, ``D act(U h)``; ``gate_up`` is then [matrices, ff, hidden].
+    ``correction`` float32 [router outputs]: added to the scores for the choice only.  ``identity``:
+    the last that many router outputs have no matrices and return the token's row times their weight.
+    ``always``: that many further units, behind the router's own in ``gate_up`` and ``down``, which every
+    token uses with weight 1; ``top`` stays the router's count, and ``chosen``, ``weight`` and ``rows``
+    hold ``top + always`` places per token, sized by the caller with moe_capacity(tokens, top + always,
+    matrices) and so on.  ``renormalize`` divides the weights by their sum + ``renorm_eps``;
+    ``route_scale`` multiplies them."""
     fn = _function("moe", "vipera_moe", [ctypes.POINTER(_MoeParams), _c_int, _c_void])
     _check_struct("moe", "vipera_moe_params_size", _MoeParams)
     tokens, hidden = h.shape
-    experts, ff = gate_up.shape[0], gate_up.shape[1] // 2
-    if tuple(router.shape) != (experts, hidden) or tuple(gate_up.shape) != (experts, 2 * ff, hidden) or \
-            tuple(down.shape) != (experts, hidden, ff) or gate_up.dtype != h.dtype or down.dtype != h.dtype:
-        raise InvalidArgumentError("moe: the experts' matrices do not match h and each other")
-    top = int(top)
+    matrices, ff = gate_up.shape[0], gate_up.shape[1] // (2 if gated else 1)
+    outputs, identity, always = router.shape[0], int(identity), int(always)
+    if outputs - identity + always != matrices or identity < 0 or always < 0 or router.shape[1] != hidden or \
+            tuple(gate_up.shape) != (matrices, (2 if gated else 1) * ff, hidden) or \
+            tuple(down.shape) != (matrices, hidden, ff) or gate_up.dtype != h.dtype or down.dtype != h.dtype:
+        raise InvalidArgumentError("moe: the experts' matrices do not match h, the router and each other")
+    if correction is not None and correction.numel() != outputs:
+        raise InvalidArgumentError("moe: one correction per router output")
+    router_top = int(top)
+    top = router_top + always      # a token's assignments
+    experts = matrices             # what the tiles are counted over
     assignments = tokens * top
-    tile_rows, padded = moe_form(tokens, top, hidden, ff, int(gate_group), h.dtype)
+    tile_rows, padded = moe_form(tokens, top, hidden, ff, int(gate_group) if gated else MOE_GATE_GROUP, h.dtype)
     if padded and (xs is None or ys is None):
         tile_rows, padded = MOE_PLAIN_ROWS, False
     tiles = moe_max_tiles(tokens, top, experts, tile_rows)
@@ -1703,7 +1788,10 @@ def moe(h: torch.Tensor, *, router: torch.Tensor, gate_up: torch.Tensor, down: t
     p.order, p.rank, p.tiles = base, base + 4 * places, base + 4 * (places + assignments)
     p.tile_expert = base + 4 * (places + assignments + 1 + 3 * most)
     p.act, p.rows = _gpu(act, "act"), _gpu(rows, "rows", torch.float32)
-    p.num_tokens, p.hidden, p.ff, p.experts, p.top = int(tokens), int(hidden), int(ff), int(experts), top
+    p.num_tokens, p.hidden, p.ff, p.experts, p.top = int(tokens), int(hidden), int(ff), int(outputs), router_top
+    p.correction = _opt(correction, "correction", torch.float32)
+    p.identity, p.always, p.slots, p.gated = identity, always, top, int(bool(gated))
+    p.route_scale, p.renorm_eps = float(route_scale), float(renorm_eps)
     p.groups, p.keep, p.group_top, p.max_tiles = int(groups), int(keep), int(group_top), int(tiles)
     p.softmax_scores, p.renormalize, p.activation = int(bool(softmax_scores)), int(bool(renormalize)), int(activation)
     p.gate_group, p.tile_rows, p.padded = int(gate_group), int(tile_rows), int(padded)
@@ -1718,7 +1806,8 @@ def moe(h: torch.Tensor, *, router: torch.Tensor, gate_up: torch.Tensor, down: t
     xs_rows = xs.view(-1)[:capacity * hidden].view(capacity, hidden)
     act_rows = act.view(-1)[:capacity * ff].view(capacity, ff)
     ys_rows = ys.view(-1)[:capacity * hidden].view(capacity, hidden)
-    gemm_tc_grouped(xs_rows, gate_up, tile_expert, epilogue=EPI_GATED, out=act_rows, activation=activation, what="moe")
+    gemm_tc_grouped(xs_rows, gate_up, tile_expert, epilogue=EPI_GATED if gated else EPI_STORE, out=act_rows,
+                    activation=activation, what="moe")
     gemm_tc_grouped(act_rows, down, tile_expert, epilogue=EPI_STORE, out=ys_rows, what="moe")
     scatter = _function("moe", "vipera_moe_scatter", [ctypes.POINTER(_MoeParams), _c_void])
     _check(scatter(ctypes.byref(p), _stream()), "moe")

@@ -39,7 +39,15 @@ class GQAttention(Mixer):
     are each divided by their root mean square and multiplied by a weight per value,
     ``<q>.norm.weight`` and ``<k>.norm.weight``, before the rotation); ``talking_heads`` (the
     softmax weights of the heads are mixed by ``<prefix>.talk.weight`` [heads, heads] before they
-    meet the values, ``w_h = sum_g M[h, g] p_g``); ``out_scale`` (multiplies the mixer's output)."""
+    meet the values, ``w_h = sum_g M[h, g] p_g``); ``out_scale`` (multiplies the mixer's output);
+    ``sink = "learned"`` (the sink's score is a number per query head, ``<prefix>.sink.weight`` [heads]:
+    ``exp(sink_h)`` joins the denominator, unscaled); ``output_gate`` (the concatenated heads are
+    multiplied by ``sigmoid(W_g h)``, ``<prefix>.<gate_name>.weight`` [heads * value_dim, hidden],
+    ``gate_name`` ``g`` by default; the gate's rows join the q/k/v product); ``value_mix``:
+    ``"source"`` publishes the values of the step's tokens as projected, ``"blend"`` caches
+    ``(1 - b) v + b v_source`` with ``b = <prefix>.vmix.weight`` (a single number) and ``v_source`` what
+    the source layer published for the same token earlier in the step (both kinds hold the tensor;
+    the source does not read it)."""
 
     kernels = ("rope_cache", "attention", "attention_mma", "attention_tc")
     takes_lazy_input = True
@@ -72,6 +80,12 @@ class GQAttention(Mixer):
             schema[f"{prefix}.{kn}.norm.weight"] = TensorSpec((kv_width,), init="norm")
         if params.get("talking_heads", False):
             schema[f"{prefix}.talk.weight"] = TensorSpec((params["num_heads"], params["num_heads"]), init="mix")
+        if params.get("sink") == "learned":
+            schema[f"{prefix}.sink.weight"] = TensorSpec((params["num_heads"],), init="sink", store="float32")
+        if params.get("output_gate", False):
+            schema[f"{prefix}.{params.get('gate_name', 'g')}.weight"] = TensorSpec((params["num_heads"] * dv, hidden))
+        if params.get("value_mix"):
+            schema[f"{prefix}.vmix.weight"] = TensorSpec((), init="blend", store="float32")
         if params.get("qkv_bias", False):
             schema[f"{prefix}.{qn}.bias"] = TensorSpec((q_width,), init="bias")
             schema[f"{prefix}.{kn}.bias"] = TensorSpec((kv_width,), init="bias")
@@ -88,6 +102,18 @@ class GQAttention(Mixer):
         self.window = params.get("window")
         self.keep_first = int(params.get("keep_first") or 0) if self.window else 0
         self.sink = bool(params.get("sink", False))
+        self.sink_values = None
+        if params.get("sink") == "learned":
+            self.sink_values = tensors[f"{prefix}.sink.weight"].to(device=device, dtype=torch.float32).contiguous()
+        elif params.get("sink") not in (None, False, True):
+            raise UnsupportedError(f"{prefix}: sink is true or \"learned\", not {params.get('sink')!r}")
+        self.gated = bool(params.get("output_gate", False))
+        self.value_mix = params.get("value_mix") or None
+        if self.value_mix not in (None, "source", "blend"):
+            raise UnsupportedError(f"{prefix}: value_mix is \"source\" or \"blend\", not {self.value_mix!r}")
+        self.blend = None
+        if self.value_mix == "blend":
+            self.blend = tensors[f"{prefix}.vmix.weight"].to(device=device, dtype=torch.float32).reshape(1).contiguous()
         self.scale = float(params["softmax_scale"])
         for size in (self.head_dim, self.value_dim):
             if not 0 < size <= 256:
@@ -106,18 +132,27 @@ class GQAttention(Mixer):
         if self.values_from_keys and self.value_dim != self.head_dim:
             raise UnsupportedError("attention: values that are the keys have the keys' size")
         if params.get("talking_heads", False):
-            if self.window or self.chunk or self.sink:
+            if self.window or self.chunk or self.sink or self.gated or self.value_mix:
                 raise UnsupportedError("attention: mixed head weights come with a plain causal mask only")
             self.talk = tensors[f"{prefix}.talk.weight"].to(device=device, dtype=torch.float32).contiguous()
         self.q_norm = self.k_norm = None
         if self.row_norm:
             self.q_norm = tensors[f"{prefix}.{qn}.norm.weight"].to(device=device, dtype=torch.float32).contiguous()
             self.k_norm = tensors[f"{prefix}.{kn}.norm.weight"].to(device=device, dtype=torch.float32).contiguous()
-        fused = torch.cat([tensors[f"{prefix}.{n}.weight"] for n in ((qn, kn) if self.values_from_keys else (qn, kn, vn))],
-                          dim=0)
+        if (self.gated or self.value_mix) and (self.values_from_keys or self.row_norm):
+            raise UnsupportedError("attention: an output gate or blended values do not come with a norm over whole "
+                                   "rows or values that are the keys")
+        names = (qn, kn) if self.values_from_keys else (qn, kn, vn)
+        # the gate reads the mixer's input like q, k and v: its rows are the last of the one product
+        self.gate_offset = sum(tensors[f"{prefix}.{n}.weight"].shape[0] for n in names)
+        if self.gated:
+            names = names + (params.get("gate_name", "g"),)
+        fused = torch.cat([tensors[f"{prefix}.{n}.weight"] for n in names], dim=0)
         bias = None
         if params.get("qkv_bias", False):
             bias = torch.cat([tensors[f"{prefix}.{n}.bias"].to(torch.float32) for n in (qn, kn, vn)], dim=0)
+            if self.gated:
+                bias = torch.cat([bias, torch.zeros(fused.shape[0] - bias.shape[0])])
         self.qkv = Linear(fused, dtype, device, bias=bias)
         self.out = Linear(tensors[f"{prefix}.{on}.weight"], dtype, device)
         position = params["position"]
@@ -128,7 +163,8 @@ class GQAttention(Mixer):
         self.common_form = (self.value_dim == self.head_dim and self.rot_dims == self.head_dim
                             and not self.keep_first and not self.sink and self.head_dim % 16 == 0
                             and not self.chunk and not self.values_from_keys and not self.row_norm
-                            and self.talk is None and self.out_scale == 1.0)
+                            and self.talk is None and self.out_scale == 1.0 and not self.gated
+                            and self.value_mix is None)
 
     def kernel_families(self):
         # the tensor-core attention kernels serve bfloat16 with head sizes 64 and 128; everything
@@ -138,7 +174,7 @@ class GQAttention(Mixer):
             own.append("attention_talk")
             if self.dtype == torch.bfloat16 and self.head_dim in ops.MMA_HEAD_DIMS and self.value_dim == self.head_dim:
                 own.append("attention_mma")
-        plain_mask = self.talk is None and self.out_scale == 1.0
+        plain_mask = self.talk is None and self.out_scale == 1.0 and self.sink_values is None and not self.gated
         if plain_mask and self.dtype == torch.bfloat16 and self.head_dim in (64, 128) and self.value_dim == self.head_dim:
             own.append("attention_mma")
             if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS and not self.keep_first and not self.sink and not self.chunk:
@@ -164,6 +200,10 @@ class GQAttention(Mixer):
         dv = params.get("value_dim") or params["head_dim"]
         q_width = params["num_heads"] * params["head_dim"]
         qkv_width = q_width + params["num_kv_heads"] * (params["head_dim"] + dv)
+        if params.get("output_gate", False):
+            qkv_width += params["num_heads"] * dv
+        if params.get("value_mix"):
+            qkv_width += params["num_kv_heads"] * dv   # the published values, 32-bit
         # q and the attention's output in the run's type, and the 32-bit q/k/v product of the unfused route
         return tokens * ((q_width + params["num_heads"] * dv) * element_bytes + qkv_width * 4)
 
@@ -228,15 +268,31 @@ class GQAttention(Mixer):
             style, cos, sin = ops.ROPE_NONE, None, None
         else:
             cos, sin = self.position.tables()
-        ops.rope_cache(qkv, q, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
-                       positions=ctx.positions, cos=cos, sin=sin, style=style,
-                       k_pool=cache.k, v_pool=cache.v, token_seq=ctx.token_entry, block_table=table,
-                       page_size=cache.page_size, write_cache=writes_cache, value_dim=dv, rot_dims=self.rot_dims)
+        if self.gated or self.value_mix:
+            publish = blend_with = None
+            if self.value_mix == "source":
+                publish = ws.get("attention.value_mix", (count, kv_heads * dv), torch.float32)
+                ctx.extras["attention.value_mix"] = publish
+            elif self.value_mix == "blend":
+                blend_with = ctx.extras.get("attention.value_mix")
+                if blend_with is None or tuple(blend_with.shape) != (count, kv_heads * dv):
+                    raise UnsupportedError(f"{self.prefix}: no earlier layer of this step published values of this "
+                                           "layer's size to blend with")
+            ops.rope_cache_blend(qkv, q, num_heads=heads, num_kv_heads=kv_heads, head_dim=d, value_dim=dv,
+                                 rot_dims=self.rot_dims if style != ops.ROPE_NONE else 0, positions=ctx.positions,
+                                 cos=cos, sin=sin, style=style, k_pool=cache.k, v_pool=cache.v,
+                                 token_seq=ctx.token_entry, block_table=table, page_size=cache.page_size,
+                                 write_cache=writes_cache, publish=publish, blend_with=blend_with, blend=self.blend)
+        else:
+            ops.rope_cache(qkv, q, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
+                           positions=ctx.positions, cos=cos, sin=sin, style=style,
+                           k_pool=cache.k, v_pool=cache.v, token_seq=ctx.token_entry, block_table=table,
+                           page_size=cache.page_size, write_cache=writes_cache, value_dim=dv, rot_dims=self.rot_dims)
         mixed = ws.get("attention.out", (count, heads * dv), ctx.dtype)
-        self._attend(ctx, q, mixed, cache, table)
+        self._attend(ctx, q, mixed, cache, table, gate=qkv if self.gated else None)
         self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
 
-    def _attend(self, ctx, q, mixed, cache, table):
+    def _attend(self, ctx, q, mixed, cache, table, gate=None):
         """Choose the attention kernel: on the bfloat16 path with a head size the tensor-core
         kernels are built for, the split-key kernel for steps of single tokens and the flash
         kernel otherwise; in every other case the general kernel."""
@@ -278,7 +334,8 @@ class GQAttention(Mixer):
                                head_dim=d, value_dim=self.value_dim, scale=self.scale, out_scale=self.out_scale,
                                split_keys=keys, num_splits=splits, stats=stats, partial=partial)
             return
-        if self.out_scale == 1.0 and ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d:
+        if (self.out_scale == 1.0 and ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d
+                and self.sink_values is None and gate is None):
             # Kept first keys and the sink are options of the mma.sync kernels (the flash kernel folds
             # the kept keys as tiles of their own, the split-key kernel as a split of its own); the
             # tcgen05 flash kernel serves attention without them.
@@ -315,7 +372,8 @@ class GQAttention(Mixer):
         ops.attention(q, mixed, cache.k, cache.v, token_seq=ctx.token_entry, positions=ctx.positions,
                       block_table=table, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
                       scale=self.scale, window=window, value_dim=self.value_dim, keep_first=self.keep_first,
-                      sink=self.sink, chunk=self.chunk, out_scale=self.out_scale)
+                      sink=self.sink, chunk=self.chunk, out_scale=self.out_scale, sink_values=self.sink_values,
+                      gate=gate, gate_offset=self.gate_offset)
 
 
 MIXERS.register("gqa_attention", GQAttention)

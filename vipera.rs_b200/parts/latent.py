@@ -36,8 +36,9 @@ HEAD_MAJOR_FROM = 64   # tokens of a step from which the up products run head by
 class LatentAttention(Mixer):
     """params: hidden_size, num_heads, head_dim (unrotated q/k values per head), rot_dim (rotated
     values per head; the key's are shared), value_dim, kv_rank, softmax_scale, norm_eps, position (a
-    PartSpec of a rotary encoding over rot_dim values) and, optionally, ``own_cache`` (default
-    true), ``output_gate`` (default false).  Tensors under ``<prefix>``: q [heads * (head_dim +
+    PartSpec of a rotary encoding over rot_dim values: interleaved pairs or halves) and, optionally,
+    ``own_cache`` (default true), ``output_gate`` (default false), ``window`` (a query at position p
+    sees keys p - window + 1 .. p; pages the window has left are given back).  Tensors under ``<prefix>``: q [heads * (head_dim +
     rot_dim), hidden], dkv [kv_rank + rot_dim, hidden] and dkv.norm [kv_rank] (with a cache of its
     own), uk [heads * head_dim, kv_rank], uv [heads * value_dim, kv_rank], g [heads * value_dim,
     hidden] (with a gate), o [hidden, heads * value_dim]."""
@@ -69,6 +70,7 @@ class LatentAttention(Mixer):
         self.scale, self.norm_eps = float(params["softmax_scale"]), float(params["norm_eps"])
         self.own_cache = bool(params.get("own_cache", True))
         self.gated = bool(params.get("output_gate", False))
+        self.window = int(params.get("window") or 0)
         if self.rank > ops.LATENT_MAX_RANK or self.rot > ops.LATENT_MAX_ROT or self.rot % 2:
             raise UnsupportedError(f"{prefix}: latent attention takes a rank up to {ops.LATENT_MAX_RANK} and an even "
                                    f"rotated part up to {ops.LATENT_MAX_ROT}")
@@ -96,8 +98,9 @@ class LatentAttention(Mixer):
         self.out = Linear(tensors[f"{prefix}.o.weight"], dtype, device)
         position = params["position"]
         self.position = POSITION_ENCODINGS.find(position.kind)(position.params, prefix, tensors, dtype, device)
-        if self.position.style != ops.ROPE_INTERLEAVED or int(getattr(self.position, "rot_dims", 0)) != self.rot:
-            raise UnsupportedError(f"{prefix}: the rotated part turns as interleaved pairs over all its {self.rot} values")
+        if self.position.style not in (ops.ROPE_INTERLEAVED, ops.ROPE_NEOX) or \
+                int(getattr(self.position, "rot_dims", 0)) != self.rot:
+            raise UnsupportedError(f"{prefix}: the rotated part turns as pairs over all its {self.rot} values")
 
     def kernel_families(self):
         grouped = ("gemm_tc",) if self.head_major else ()
@@ -108,7 +111,7 @@ class LatentAttention(Mixer):
 
     @classmethod
     def cache_request_for(cls, params):
-        return PagedKV(1, int(params["kv_rank"]), None, value_dim=int(params["rot_dim"]))
+        return PagedKV(1, int(params["kv_rank"]), params.get("window") or None, value_dim=int(params["rot_dim"]))
 
     @classmethod
     def workspace_bytes(cls, params, tokens, element_bytes):
@@ -131,6 +134,7 @@ class LatentAttention(Mixer):
         mixed = ws.get("latent.out", (count, self.heads * self.vdim), ctx.dtype)
         cos, sin = self.position.tables()
         max_keys = max(int(ctx.max_kv_len), 1)
+        # (with a window the splits past it see no key and leave at once; the combine skips them)
         floats = ops.latent_part_floats(count, self.heads, self.rank, max_keys, ops.sm_count(h.device)) if ctx.dtype == torch.bfloat16 else 0
         part = ws.get("latent.part", (floats,), torch.float32) if floats else None
         head_major = None
@@ -150,7 +154,7 @@ class LatentAttention(Mixer):
                              token_entry=ctx.token_entry, block_table=ctx.block_tables[cache.group], cos=cos, sin=sin,
                              k_pool=cache.k, v_pool=cache.v, qa=qa, latent_out=mixed_latent, out=mixed, heads=self.heads,
                              head_dim=self.dim, rot_dim=self.rot, value_dim=self.vdim, scale=self.scale, max_keys=max_keys,
-                             part=part, head_major=head_major)
+                             part=part, head_major=head_major, window=self.window, pairing=self.position.style)
         self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
 
 

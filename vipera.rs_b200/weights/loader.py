@@ -30,6 +30,9 @@ INIT = {
     "mix": (0.3, 0.4),        # a matrix that mixes heads
     "filter": (0.0, 0.3),     # taps of a short convolution
     "log_rate": (0.0, 0.5),   # logarithms of decay rates
+    "sink": (0.0, 1.5),       # learned sink scores of a softmax
+    "blend": (0.35, 0.1),     # a number that blends two tensors
+    "correction": (0.0, 0.05),  # what a router adds to its scores before it chooses
 }
 
 # An extent a part leaves open (None in a TensorSpec's shape: the tensor's own shape decides)
