@@ -738,6 +738,91 @@ def pugovik_decode_bytes(config, batch, history, element=2):
     return {"weights": weights * element, "state": state, "cache": int(cache)}
 
 
+# ---------------------------------------------------------------------------------------
+# --design fasolorn: the Fasolorn design beside the Qwen2 decoder at equal sizes
+# ---------------------------------------------------------------------------------------
+def fasolorn_config(width, heads, kv_heads, ff, layers, vocab, *_unused, experts=16, identity=2, top=4, window=1024):
+    """`layers` layers in the proportion three of grouped-query attention (heads of 128, a learned sink,
+    an output gate, values blended with the first layer's, a window) to one of attention over a cached
+    latent of 512 (heads of 128 + 64 turning values, the same window); feed-forwards by turns a gated
+    unit of the dense inner size and a mixture of `experts` units without a gate plus `identity` outputs
+    that return their input, of which a token uses `top`, beside a shared unit; a token's experts and
+    the shared unit together have two thirds of the dense inner size (units without a gate have two
+    matrices where a gated one has three)."""
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "mask": {"size": window}, "rot": {"dims": 128, "base": 500000.0}, "v_mix": True}
+    latent = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+              "mask": {"size": window}, "rot": {"dims": 64, "base": 10000.0}}
+    piece = ff // (top + 1) // 16 * 16
+    moe = {"kind": "moe", "expert": {"ff": piece}, "shared": {"ff": piece},
+           "router": {"experts": experts, "identity": identity, "top": top, "scale": 2.5}}
+    dense = {"kind": "dense", "ff": ff}
+    order = []
+    for index in range(layers):
+        mixer = ("latent_attention", latent) if index % 4 == 3 else ("attention", attention)
+        order.append({"type": mixer[0], "mixer": mixer[1], "mlp": moe if index % 2 else dense})
+    return {"architecture": "Fasolorn", "vocab": vocab, "width": width, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "layers": order}
+
+
+def fasolorn_work(config, tokens):
+    """Floating-point operations of a prompt of `tokens` tokens by class of kernel: products (the mixers'
+    matrices, the dense feed-forwards, the output matrix), the chosen experts with the shared unit and
+    the router, and attention within the windows (over keys and values, or over the latents: scores
+    against rank + rot_dim values, weighted sums of rank values, the two absorbed matrices per query)."""
+    width = config["width"]
+    flops = {"proj": 2.0 * config["vocab"] * width, "attention": 0.0, "experts": 0.0}
+    for layer in config["layers"]:
+        m = layer["mixer"]
+        window = m["mask"]["size"] if m.get("mask") else tokens
+        seen = sum(min(position + 1, window) for position in range(tokens))     # (query, key) pairs
+        if layer["type"] == "attention":
+            h, g, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            flops["proj"] += 2.0 * tokens * width * (h * d + g * (d + dv) + 2 * h * dv)
+            flops["attention"] += 2.0 * seen * h * (d + dv)
+        else:
+            h, d, r, dv, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            flops["proj"] += 2.0 * tokens * width * (h * (d + r) + rank + r + h * dv)
+            flops["attention"] += 2.0 * h * (seen * (2 * rank + r) + tokens * rank * (d + dv))
+        mlp = layer.get("mlp")
+        if mlp and mlp["kind"] == "dense":
+            flops["proj"] += 2.0 * tokens * 3 * width * mlp["ff"]
+        elif mlp:
+            router = mlp["router"]
+            inner = router["top"] * mlp["expert"]["ff"] + (mlp.get("shared") or {"ff": 0})["ff"]
+            flops["experts"] += 2.0 * tokens * (2 * width * inner + (router["experts"] + router.get("identity", 0)) * width)
+    return flops
+
+
+def fasolorn_decode_bytes(config, batch, history, element=2):
+    """What one decode step must move: every matrix a token of the batch can use (all experts once the
+    batch's choices cover them: min(experts, batch * top)), and the keys, values and latents within the
+    windows."""
+    width = config["width"]
+    weights = config["vocab"] * width
+    cache = 0
+    for layer in config["layers"]:
+        m = layer["mixer"]
+        keys = min(history, m["mask"]["size"]) if m.get("mask") else history
+        if layer["type"] == "attention":
+            h, g, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            weights += width * (h * d + g * (d + dv) + 2 * h * dv)
+            cache += batch * keys * g * (d + dv) * element
+        else:
+            h, d, r, dv, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            weights += width * (h * (d + r) + rank + r + h * dv) + h * rank * (d + dv)
+            cache += batch * keys * (rank + r) * element
+        mlp = layer.get("mlp")
+        if mlp and mlp["kind"] == "dense":
+            weights += 3 * width * mlp["ff"]
+        elif mlp:
+            router = mlp["router"]
+            used = min(router["experts"], batch * router["top"])
+            weights += 2 * width * (used * mlp["expert"]["ff"] + (mlp.get("shared") or {"ff": 0})["ff"])
+            weights += (router["experts"] + router.get("identity", 0)) * width * 2     # the router's matrix is 32-bit
+    return {"weights": weights * element, "state": 0, "cache": int(cache)}
+
+
 DESIGNS = {
     "nobupel": (lambda *sizes: nobupel_config(*sizes), lambda config, tokens: nobupel_work(config, tokens),
                 lambda config, batch, history: nobupel_decode_bytes(config, batch, history)),
@@ -745,6 +830,8 @@ DESIGNS = {
                 lambda config, batch, history: gusolix_decode_bytes(config, batch, history)),
     "pugovik": (lambda *sizes: pugovik_config(*sizes), lambda config, tokens: pugovik_work(config, tokens),
                 lambda config, batch, history: pugovik_decode_bytes(config, batch, history)),
+    "fasolorn": (lambda *sizes: fasolorn_config(*sizes), lambda config, tokens: fasolorn_work(config, tokens),
+                 lambda config, batch, history: fasolorn_decode_bytes(config, batch, history)),
 }
 
 

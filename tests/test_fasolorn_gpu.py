@@ -1,0 +1,362 @@
+"""Fasolorn on the GPU against the plain implementation: each mechanism alone, prompts against
+token-by-token decoding, portions down to two tokens, batches against each request alone, pages used
+again, keys far away, at page borders and just inside and outside every window, the first tokens of a
+request, long decoding, other sizes, long steps of a larger model, the replayer as a process, greedy
+generation through the engine and the command line."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import fasolorn_cases as cases
+import helpers
+from helpers import TraceBuilder
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 5e-4   # of the request's largest |logit|; the sharpened weights amplify rounding
+# bfloat16 rows are judged together: median, 95th percentile and worst of the error's root mean square
+# over the vocabulary (mean taken off), relative to the logits' own root mean square.  A choice of
+# experts that rounding tips shows as one large error at that position: few may be.
+BF16_MEDIAN, BF16_MOST, BF16_FEW, BF16_WORST = 3e-2, 8e-2, 0.15, 0.6
+CLOSE_CALL = 0.01   # of router scores plus corrections
+
+
+def replayer(path, dtype, max_tokens, page_size=16, max_live=4):
+    import vipera_rs_b200  # noqa: F401
+    from vipera_rs_b200.engine.replay import Replayer
+
+    rp = Replayer(path, dtype, max_tokens=max_tokens, page_size=page_size, max_live=max_live)
+    rp.pools.poison()
+    return rp
+
+
+class Judge:
+    """Rows of one request against the plain implementation's.  In bfloat16 a position where a plain
+    router's choice hangs on less than CLOSE_CALL may come out with other experts: it must be finite
+    and is left out of the statistics; few positions may be such."""
+
+    def __init__(self, dtype, path, tokens, most_skipped=0.4):
+        self.dtype, self.most_skipped = dtype, most_skipped
+        self.want = cases.plain_logits(path, tokens)
+        self.close_call = cases.plain_margins(path, tokens) < CLOSE_CALL
+        self.scale = float(np.abs(self.want).max())
+        centred = self.want - self.want.mean(axis=-1, keepdims=True)
+        self.rms = float(np.sqrt((centred ** 2).mean()))
+        self.errors, self.skipped = [], 0
+
+    def add(self, got, first, where=None):
+        """`got` [n, vocab] are the rows of positions first .. first + n - 1."""
+        got = np.atleast_2d(got)
+        want = self.want[first:first + got.shape[0]]
+        assert got.shape == want.shape and np.isfinite(got).all(), where
+        if self.dtype == "float32":
+            error = float(np.abs(got - want).max()) / self.scale
+            assert error <= FP32_TOL, (where, first, error)
+            return
+        diff = got - want
+        diff = diff - diff.mean(axis=-1, keepdims=True)
+        for row, error in enumerate((np.sqrt((diff ** 2).mean(axis=-1)) / self.rms).tolist()):
+            if self.close_call[first + row]:
+                self.skipped += 1
+            else:
+                self.errors.append(error)
+
+    def close(self):
+        if self.dtype == "float32":
+            return
+        assert self.errors and self.skipped <= self.most_skipped * (self.skipped + len(self.errors)), (self.skipped, len(self.errors))
+        errors = np.sort(np.asarray(self.errors))
+        median, most, worst = np.median(errors), errors[int(0.95 * (len(errors) - 1))], errors[-1]
+        tipped = int((errors > BF16_FEW).sum())
+        assert median <= BF16_MEDIAN and most <= BF16_MOST and worst <= BF16_WORST and tipped <= max(1, len(errors) // 50), \
+            (median, most, worst, tipped)
+
+
+def folder_for(name, dtype, sharp="sharp"):
+    """Sharpened weights in 32-bit, where an edge that is one off must show; milder ones in bfloat16."""
+    return cases.folder(name, dtype, scaling=sharp if dtype == "float32" else "mild")
+
+
+def whole(rp, name, tokens):
+    return rp.step([{"id": name, "tokens": list(tokens), "want": list(range(len(tokens)))}], [name])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["attention", "blend", "latent", "moe"])
+def test_each_mechanism_alone(name, dtype):
+    path = folder_for(name, dtype)
+    tokens = helpers.random_tokens(cases.CONFIGS[name]["vocab"], 77, 9)
+    rp = replayer(path, dtype, 128)
+    judge = Judge(dtype, path, tokens)
+    judge.add(whole(rp, "a", tokens), 0)
+    judge.close()
+    assert rp.pools.audit() == ""
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["mixed", "wide"])
+def test_prompt_against_decoding_and_portions(name, dtype):
+    """The same request whole, token by token from the first token on (every window passes over decoded
+    tokens), and in portions of changing size, down to two tokens."""
+    path = folder_for(name, dtype)
+    length = 150
+    tokens = helpers.random_tokens(cases.CONFIGS[name]["vocab"], length, 21)
+    rp = replayer(path, dtype, 2 * 160)
+    judge = Judge(dtype, path, tokens)
+    judge.add(whole(rp, "whole", tokens), 0, "whole")
+    judge.close()
+    judge = Judge(dtype, path, tokens)
+    for position in range(length):
+        got = rp.step([{"id": "one", "tokens": tokens[position:position + 1], "want": [0]}],
+                      ["one"] if position == length - 1 else [])
+        judge.add(got, position, "decoding")
+    judge.close()
+    judge = Judge(dtype, path, tokens)
+    done = 0
+    for turn, size in enumerate([2, 31, 2, 3, 16, 17, 1, 1, 40, 2, 5, 30]):
+        size = min(size, length - done)
+        got = rp.step([{"id": "cut", "tokens": tokens[done:done + size], "want": list(range(size))}],
+                      ["cut"] if done + size == length else [])
+        judge.add(got, done, ("portion", turn))
+        done += size
+    judge.close()
+    assert done == length and rp.pools.audit() == ""
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_window_edges_and_page_borders_in_prompts_and_decoding(dtype):
+    """Windows of 17, 21, 24 and 30 keys over pages of 8 (the CPU tests show that each window moved by
+    one key moves the logits): portions that end inside, at and just behind a page's border and a
+    window's edge, then token by token while every window passes over decoded tokens and pages the
+    windows have left are given back and handed out again."""
+    path = folder_for("mixed", dtype)
+    tokens = helpers.random_tokens(cases.MIXED["vocab"], 200, 31)
+    judge = Judge(dtype, path, tokens)
+    rp = replayer(path, dtype, 208, page_size=8)
+    done = 0
+    for size in (7, 1, 1, 7, 1, 4, 2, 1, 6, 2, 33, 63):     # ends at 7, 8, 9, 16, 17, 21, 23, 24, 30, 32, 65, 128
+        got = rp.step([{"id": "p", "tokens": tokens[done:done + size], "want": list(range(size))}], [])
+        judge.add(got, done, "portion")
+        done += size
+    for position in range(done, len(tokens)):
+        got = rp.step([{"id": "p", "tokens": tokens[position:position + 1], "want": [0]}],
+                      ["p"] if position == len(tokens) - 1 else [])
+        judge.add(got, position, "decoding")
+    judge.close()
+    assert rp.pools.audit() == ""
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_far_keys_without_masks(dtype):
+    """No layer has a mask (the CPU tests show that token 3 moves the logits 250 tokens later): portions
+    across page borders, then decoding."""
+    path = folder_for("far", dtype)
+    tokens = helpers.random_tokens(cases.FAR["vocab"], 260, 6)
+    judge = Judge(dtype, path, tokens)
+    rp = replayer(path, dtype, 272, page_size=16)
+    done = 0
+    for size in (15, 2, 111, 2, 90):
+        got = rp.step([{"id": "p", "tokens": tokens[done:done + size], "want": list(range(size))}], [])
+        judge.add(got, done, "portion")
+        done += size
+    for position in range(done, len(tokens)):
+        got = rp.step([{"id": "p", "tokens": tokens[position:position + 1], "want": [0]}],
+                      ["p"] if position == len(tokens) - 1 else [])
+        judge.add(got, position, "decoding")
+    judge.close()
+    assert rp.pools.audit() == ""
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["mixed", "wide"])
+def test_batches_of_unequal_requests_with_pages_used_again(name, dtype):
+    """Up to four live requests, portions beside single tokens, requests left out of steps; the pool
+    holds little more than the live requests, so pages go from request to request."""
+    path = folder_for(name, dtype)
+    vocab = cases.CONFIGS[name]["vocab"]
+    lengths = [90, 61, 130, 47, 75, 38]
+    requests = {f"r{i}": helpers.random_tokens(vocab, n, 40 + i) for i, n in enumerate(lengths)}
+    judges = {rid: Judge(dtype, path, tokens) for rid, tokens in requests.items()}
+    page = 16
+    rounded = sorted(((n + page - 1) // page * page for n in lengths), reverse=True)
+    rp = replayer(path, dtype, sum(rounded[:4]), page_size=page, max_live=4)
+    state = {rid: 0 for rid in requests}
+    waiting, live, turn = list(requests), [], 0
+    while waiting or live:
+        while waiting and len(live) < 4:
+            live.append(waiting.pop(0))
+        entries, ended, expect = [], [], []
+        for slot, rid in enumerate(list(live)):
+            tokens, done = requests[rid], state[rid]
+            prompt = len(tokens) - 12
+            if done < prompt:
+                size = min([23, 2, 40, 9][(turn + slot) % 4], prompt - done)
+                if (turn + slot) % 5 == 4:
+                    continue
+            else:
+                size = 1
+            entries.append({"id": rid, "tokens": tokens[done:done + size], "want": list(range(size))})
+            expect.append((rid, done, size))
+            state[rid] = done + size
+            if state[rid] == len(tokens):
+                ended.append(rid)
+                live.remove(rid)
+        turn += 1
+        if not entries:
+            continue
+        got = rp.step(entries, ended)
+        row = 0
+        for rid, done, size in expect:
+            judges[rid].add(got[row:row + size], done, (rid, done, size))
+            row += size
+    for judge in judges.values():
+        judge.close()
+    assert rp.pools.audit() == ""
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_steps_of_a_larger_model(dtype):
+    """Steps of hundreds of tokens (the forms of the kernels that long steps take): two requests of
+    unequal length in one step, then a portion of one beside a single token of the other, then both
+    token by token."""
+    path = folder_for("large", dtype, sharp="mild")
+    vocab = cases.LARGE["vocab"]
+    long, short = helpers.random_tokens(vocab, 760, 3), helpers.random_tokens(vocab, 150, 4)
+    judges = {"long": Judge(dtype, path, long, most_skipped=0.6), "short": Judge(dtype, path, short, most_skipped=0.6)}
+    rp = replayer(path, dtype, 768 + 192, page_size=16)
+    wanted = list(range(0, 650, 7))
+    got = rp.step([{"id": "long", "tokens": long[:650], "want": wanted},
+                   {"id": "short", "tokens": short[:131], "want": list(range(131))}], [])
+    for row, position in enumerate(wanted):
+        judges["long"].add(got[row], position, ("long", position))
+    judges["short"].add(got[len(wanted):], 0, "short")
+    got = rp.step([{"id": "long", "tokens": long[650:745], "want": list(range(95))},
+                   {"id": "short", "tokens": short[131:132], "want": [0]}], [])
+    judges["long"].add(got[:95], 650, "long portion")
+    judges["short"].add(got[95], 131, "short single")
+    for step in range(15):
+        got = rp.step([{"id": "long", "tokens": long[745 + step:746 + step], "want": [0]},
+                       {"id": "short", "tokens": short[132 + step:133 + step], "want": [0]}],
+                      ["long", "short"] if step == 14 else [])
+        judges["long"].add(got[0], 745 + step, ("long", step))
+        judges["short"].add(got[1], 132 + step, ("short", step))
+    for judge in judges.values():
+        judge.close()
+    assert rp.pools.audit() == ""
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_other_sizes(dtype):
+    """Sizes and options the other configurations lack (see fasolorn_cases): whole, in portions with a
+    second request beside it, and decoding; the first tokens of a request one by one."""
+    # (in bfloat16 unscaled weights: at these sizes the scaled ones turn one position's rounding into
+    # tens of percent, alike however the request is cut)
+    path = cases.folder("odd", dtype, scaling="mild" if dtype == "float32" else "none")
+    vocab = cases.ODD["vocab"]
+    a, b = helpers.random_tokens(vocab, 83, 71), helpers.random_tokens(vocab, 29, 72)
+    rp = replayer(path, dtype, 256, page_size=8)
+    judge, judge_b = Judge(dtype, path, a), Judge(dtype, path, b)
+    judge.add(whole(rp, "whole", a), 0, "whole")
+    done_a = done_b = 0
+    for size_a, size_b in ((1, 3), (1, 1), (2, 1), (5, 1), (30, 2), (1, 21), (43, 0)):
+        entries = [{"id": "a", "tokens": a[done_a:done_a + size_a], "want": list(range(size_a))}]
+        if size_b:
+            entries.append({"id": "b", "tokens": b[done_b:done_b + size_b], "want": list(range(size_b))})
+        got = rp.step(entries, ["b"] if done_b + size_b == len(b) and size_b else [])
+        judge.add(got[:size_a], done_a, ("a", done_a))
+        if size_b:
+            judge_b.add(got[size_a:], done_b, ("b", done_b))
+        done_a, done_b = done_a + size_a, done_b + size_b
+    assert done_a == len(a) and done_b == len(b)
+    judge.close()
+    judge_b.close()
+    assert rp.pools.audit() == ""
+
+
+def test_long_decoding_of_several_requests():
+    """Three requests decode 200 tokens each side by side after prompts of unequal length (replayed
+    decode graphs with a padded entry; every window passes over decoded tokens many times)."""
+    dtype = "float32"
+    path = folder_for("mixed", dtype)
+    vocab = cases.MIXED["vocab"]
+    prompts = {"a": 17, "b": 3, "c": 40}
+    requests = {rid: helpers.random_tokens(vocab, n + 200, 80 + n) for rid, n in prompts.items()}
+    judges = {rid: Judge(dtype, path, requests[rid]) for rid in requests}
+    rp = replayer(path, dtype, 3 * 256, page_size=16)
+    got = rp.step([{"id": rid, "tokens": requests[rid][:n], "want": [n - 1]} for rid, n in prompts.items()], [])
+    for row, (rid, n) in enumerate(prompts.items()):
+        judges[rid].add(got[row], n - 1, (rid, "prompt"))
+    for step in range(200):
+        got = rp.step([{"id": rid, "tokens": requests[rid][n + step:n + step + 1], "want": [0]} for rid, n in prompts.items()],
+                      list(prompts) if step == 199 else [])
+        for row, (rid, n) in enumerate(prompts.items()):
+            judges[rid].add(got[row], n + step, (rid, step))
+    assert rp.runner.graph_replays > 150 and rp.pools.audit() == ""
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_as_a_process(dtype):
+    path = folder_for("mixed", dtype)
+    vocab = cases.MIXED["vocab"]
+    a, b = helpers.random_tokens(vocab, 50, 1), helpers.random_tokens(vocab, 21, 2)
+    builder = TraceBuilder()
+    builder.step([("a", a[:30], [0, 29]), ("b", b[:2], [1])])
+    builder.step([("a", a[30:31], [0]), ("b", b[2:], list(range(19)))], end=["b"])
+    builder.step([("a", a[31:], list(range(19)))], end=["a"])
+    outputs = helpers.run_trace(path, dtype, builder.steps, max_tokens=128, page_size=16, max_live=4, vocab=vocab)
+    reference = {"a": cases.plain_logits(path, a), "b": cases.plain_logits(path, b)}
+    close_calls = set()
+    if dtype == "bfloat16":   # where a plain router's choice hangs on a hair, bfloat16 may choose otherwise
+        for name, tokens in (("a", a), ("b", b)):
+            close_calls.update((name, int(p)) for p in np.where(cases.plain_margins(path, tokens) < CLOSE_CALL)[0])
+        assert len(close_calls) < 30
+    helpers.compare(outputs, builder, reference, FP32_TOL if dtype == "float32" else 0.08, f"fasolorn {dtype}",
+                    exempt=close_calls, most=1.0 if dtype == "float32" else 0.9)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_engine(dtype):
+    import vipera_rs_b200  # noqa: F401
+    from vipera_rs_b200 import Engine, SamplingParams
+
+    path = cases.folder("wide", dtype, scaling="none")
+    vocab = cases.WIDE["vocab"]
+    prompts = [helpers.random_tokens(vocab, n, 60 + n) for n in (70, 9, 33)]
+    engine = Engine(path, dtype=dtype, page_size=16, ctx=128, max_num_seqs=2, max_portion=32)
+    results = engine.generate(prompts, SamplingParams(max_new_tokens=20))
+    for prompt, result in zip(prompts, results):
+        produced = result.tokens
+        assert len(produced) == 20
+        logits = cases.plain_logits(path, prompt + produced[:-1])
+        tipped = 0
+        for index, token in enumerate(produced):
+            row = logits[len(prompt) - 1 + index]
+            margin = float(row.max() - row[token]) / float(np.abs(row).max())
+            if dtype == "bfloat16" and 3e-2 < margin <= 0.3:
+                tipped += 1   # rounding chose other experts at this token; the continuation is judged on what was produced
+                continue
+            assert margin <= (1e-4 if dtype == "float32" else 3e-2), (index, token)
+        assert tipped <= 2
+    assert engine.pools.audit() == ""
+
+
+def test_generate_from_the_command_line():
+    """bin/vipera model-info, plan and generate on a Fasolorn folder: each token of the greedy
+    continuation is the plain implementation's best (or within rounding of it)."""
+    path = cases.folder("mixed", "float32", scaling="none")
+    tool = os.path.join(helpers.ROOT, "bin", "vipera")
+    info = subprocess.run([sys.executable, tool, "model-info", path], capture_output=True, text=True, timeout=600)
+    assert info.returncode == 0 and "Fasolorn" in info.stdout, info.stderr[-2000:]
+    prompt = [5, 17, 3, 200, 41, 77, 110, 9]
+    result = subprocess.run([sys.executable, tool, "generate", path, "--prompt", " ".join(str(t) for t in prompt),
+                             "--max-tokens", "10", "--dtype", "float32"], capture_output=True, text=True, timeout=900)
+    assert result.returncode == 0, result.stderr[-2000:]
+    produced = [int(word) for word in result.stdout.split() if word.isdigit()][:10]
+    assert len(produced) == 10
+    logits = cases.plain_logits(path, prompt + produced[:-1])
+    for index, token in enumerate(produced):
+        row = logits[len(prompt) - 1 + index]
+        assert float(row.max() - row[token]) <= 1e-4 * float(np.abs(row).max()), (index, token)
