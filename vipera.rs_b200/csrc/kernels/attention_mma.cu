@@ -379,7 +379,12 @@ template <int D, bool KEPT = false, bool WIDE = false>
 __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, const float* __restrict__ partial_out,
                                          int slices, __nv_bfloat16* __restrict__ out, int num_heads,
                                          const int* __restrict__ positions, int window, int chunk,
-                                         const int* __restrict__ entry_starts, int keep_first, int sink) {
+                                         const int* __restrict__ entry_starts, int keep_first, int sink,
+                                         const float* __restrict__ sink_values = nullptr,
+                                         const float* __restrict__ gate = nullptr, long long gate_stride = 0) {
+  // KEPT instances also know a learned sink (`sink_values` [heads]: exp(sink_h) joins head h's sum
+  // instead of one) and an output gate (`gate`: the row of the entry's token, at gate + token *
+  // gate_stride, holds [heads * D] 32-bit pre-activations whose sigmoid multiplies the output).
   // `slices` counts the window's splits; with kept first keys (keep_first > 0) each row has one
   // more place, the last, for the kept keys the window has left behind.  sink != 0: a key of score
   // 0 without a value joins the softmax, which adds exp2(-max) to the sum.
@@ -389,10 +394,12 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
   // the step's description (written by the host before the step) is read before the wait
   const size_t row = static_cast<size_t>(blockIdx.x) * num_heads + blockIdx.y;
   size_t out_row = row;
+  size_t out_token = blockIdx.x;
   if (entry_starts) {   // a step with portions: only entries of one token, written at their token's row
     const int token = entry_starts[blockIdx.x];
     if (entry_starts[blockIdx.x + 1] - token != 1) return;
     out_row = static_cast<size_t>(token) * num_heads + blockIdx.y;
+    out_token = static_cast<size_t>(token);
   }
   const int places = slices + ((KEPT && keep_first > 0) ? 1 : 0);
   const float* ml = partial_ml + 2 * row * places;
@@ -445,9 +452,11 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
       value += values[static_cast<size_t>(place_of(s)) * D] * w;
     }
   }
-  if (KEPT && sink) total += exp2f(-mine);   // the maxima are in units of log2
-  if (WIDE) reinterpret_cast<float*>(out)[out_row * D + threadIdx.x] = value / total;
-  else out[out_row * D + threadIdx.x] = __float2bfloat16_rn(value / total);
+  if (KEPT && sink) total += sink_values ? exp2f(sink_values[blockIdx.y] * 1.4426950408889634f - mine) : exp2f(-mine);   // the maxima are in units of log2
+  float result = value / total;
+  if (KEPT && gate) result *= 1.0f / (1.0f + expf(-gate[out_token * gate_stride + static_cast<size_t>(blockIdx.y) * D + threadIdx.x]));
+  if (WIDE) reinterpret_cast<float*>(out)[out_row * D + threadIdx.x] = result;
+  else out[out_row * D + threadIdx.x] = __float2bfloat16_rn(result);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -781,7 +790,8 @@ template <int D>
 int launch_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int* positions,
                   const int* block_table, int table_width, int page_size, int num_entries, int num_heads,
                   int num_kv_heads, float scale, int window, int chunk, int num_splits, float* partial_ml,
-                  float* partial_out, const int* entry_starts, int keep_first, int sink, cudaStream_t s) {
+                  float* partial_out, const int* entry_starts, int keep_first, int sink, cudaStream_t s,
+                  const float* sink_values = nullptr, const float* gate = nullptr, long long gate_stride = 0) {
   constexpr int kSmem = 16 * D * 2 + 4 * 2 * 32 * D * 2;
   int page_shift = -1;
   if ((page_size & (page_size - 1)) == 0) {
@@ -789,7 +799,7 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
     while ((1 << page_shift) < page_size) ++page_shift;
   }
   // the one-kernel forms serve steps of single tokens only
-  const ClusterChoice cluster = (entry_starts || keep_first > 0 || sink) ? ClusterChoice{0, false}
+  const ClusterChoice cluster = (entry_starts || keep_first > 0 || sink || gate) ? ClusterChoice{0, false}
                                              : cluster_decode_choice(num_entries, num_heads, num_kv_heads, chunk * num_splits);
   if (cluster.blocks == 8 && cluster.prefetch)
     return launch_decode_cluster<D, 8, true>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size,
@@ -811,7 +821,7 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  if (keep_first > 0 || sink) {
+  if (keep_first > 0 || sink || gate) {
     dim3 grid(num_entries, num_kv_heads, num_splits + (keep_first > 0 ? 1 : 0));
     int status = vipera_launch(attention_decode_kernel<D, true>, grid, 128, kSmem, s,
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pool),
@@ -820,7 +830,8 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
     if (status != VIPERA_OK) return status;
     return vipera_launch(attention_combine_kernel<D, true>, dim3(num_entries, num_heads), D, 0, s,
         static_cast<const float*>(partial_ml), static_cast<const float*>(partial_out), num_splits,
-        static_cast<__nv_bfloat16*>(out), num_heads, positions, window, chunk, entry_starts, keep_first, sink);
+        static_cast<__nv_bfloat16*>(out), num_heads, positions, window, chunk, entry_starts, keep_first, sink,
+        sink_values, gate, gate_stride);
   }
   dim3 grid(num_entries, num_kv_heads, num_splits);
   int status = vipera_launch(attention_decode_kernel<D>, grid, 128, kSmem, s,
@@ -830,7 +841,8 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
   if (status != VIPERA_OK) return status;
   return vipera_launch(attention_combine_kernel<D>, dim3(num_entries, num_heads), D, 0, s,
       static_cast<const float*>(partial_ml), static_cast<const float*>(partial_out), num_splits,
-      static_cast<__nv_bfloat16*>(out), num_heads, positions, window, chunk, entry_starts, 0, 0);
+      static_cast<__nv_bfloat16*>(out), num_heads, positions, window, chunk, entry_starts, 0, 0,
+      static_cast<const float*>(nullptr), static_cast<const float*>(nullptr), 0LL);
 }
 
 // Single tokens, every query head against every KV head's values: out [entries, heads * kv_heads, D].
@@ -861,7 +873,8 @@ int launch_decode_pairs(const void* q, void* out, const void* k_pool, const void
   if (status != VIPERA_OK) return status;
   return vipera_launch(attention_combine_kernel<D, false, true>, dim3(num_entries, pairs), D, 0, s,
       static_cast<const float*>(partial_ml), static_cast<const float*>(partial_out), num_splits,
-      static_cast<__nv_bfloat16*>(out), pairs, positions, 0, chunk, static_cast<const int*>(nullptr), 0, 0);
+      static_cast<__nv_bfloat16*>(out), pairs, positions, 0, chunk, static_cast<const int*>(nullptr), 0, 0,
+      static_cast<const float*>(nullptr), static_cast<const float*>(nullptr), 0LL);
 }
 
 }  // namespace
@@ -943,8 +956,10 @@ VIPERA_API size_t vipera_attention_decode_scratch(int num_entries, int num_heads
 static int run_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int* positions,
                       const int* block_table, int table_width, int page_size, int num_entries, int num_heads,
                       int num_kv_heads, int head_dim, float scale, int window, int chunk, int num_splits, float* scratch,
-                      size_t scratch_floats, const int* entry_starts, int keep_first, int sink, void* stream) {
+                      size_t scratch_floats, const int* entry_starts, int keep_first, int sink, void* stream,
+                      const float* sink_values = nullptr, const float* gate = nullptr, long long gate_stride = 0) {
   if (num_entries <= 0) return VIPERA_OK;
+  if (sink_values) sink = 1;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || keep_first < 0) return VIPERA_BAD_SHAPE;
   if (chunk <= 0 || chunk % 32 || num_splits <= 0 || num_splits > 128) return VIPERA_BAD_ARGUMENT;
   if (window <= 0) keep_first = 0;
@@ -959,11 +974,11 @@ static int run_decode(const void* q, void* out, const void* k_pool, const void* 
   if (head_dim == 128)
     return launch_decode<128>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries,
                               num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out,
-                              entry_starts, keep_first, sink, s);
+                              entry_starts, keep_first, sink, s, sink_values, gate, gate_stride);
   if (head_dim == 64)
     return launch_decode<64>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries,
                              num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out,
-                             entry_starts, keep_first, sink, s);
+                             entry_starts, keep_first, sink, s, sink_values, gate, gate_stride);
   return VIPERA_BAD_SHAPE;
 }
 
@@ -1016,6 +1031,21 @@ VIPERA_API int vipera_attention_decode_kept(const void* q, void* out, const void
   return run_decode(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries, num_heads,
                     num_kv_heads, head_dim, scale, window, chunk, num_splits, scratch, scratch_floats, entry_starts,
                     keep_first, sink, stream);
+}
+
+// The same with a learned sink per query head (`sink_values` [heads], null: the plain sink flag counts)
+// and an output gate (`gate`, null: none: 32-bit pre-activations, the row of token t at gate + t *
+// gate_stride holding [heads * d] values; t is the entry's index, or its token's with `entry_starts`).
+VIPERA_API int vipera_attention_decode_gated(const void* q, void* out, const void* k_pool, const void* v_pool,
+                                             const int* positions, const int* block_table, int table_width,
+                                             int page_size, int num_entries, int num_heads, int num_kv_heads,
+                                             int head_dim, float scale, int window, int chunk, int num_splits,
+                                             float* scratch, size_t scratch_floats, const int* entry_starts,
+                                             int keep_first, int sink, const float* sink_values, const float* gate,
+                                             long long gate_stride, void* stream) {
+  return run_decode(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries, num_heads,
+                    num_kv_heads, head_dim, scale, window, chunk, num_splits, scratch, scratch_floats, entry_starts,
+                    keep_first, sink, stream, sink_values, gate, gate_stride);
 }
 
 VIPERA_API const char* vipera_attention_mma_status_text(int status) { return vipera_status_text(status); }

@@ -74,6 +74,12 @@ struct Params {
   float scale;
   int skip_single;             // entries of one token are left out (the split-key kernel runs them)
   int* status;
+  // Options of the ending.  sink_values [heads] (null: none): exp(sink_h) joins head h's denominator
+  // (a learned sink: no key, no value, not scaled).  gate (null: none): the output is multiplied by
+  // sigmoid(gate[t * gate_stride + h * d + e]), a 32-bit pre-activation.
+  const float* sink_values;
+  const float* gate;
+  long long gate_stride;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -270,7 +276,9 @@ struct Barriers {
   Job job;
 };
 
-template <int D, bool TMA_KV>
+// EXT: the ending knows the learned sink and the output gate; the instances without it are the kernel
+// as it was before those options existed.
+template <int D, bool TMA_KV, bool EXT = false>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                             const __grid_constant__ CUtensorMap k_run_map, const __grid_constant__ CUtensorMap v_run_map,
@@ -481,7 +489,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       const float joint_max = fmaxf(row_max, other.x);
       const float own_weight = row_max == -INFINITY ? 0.0f : fast_exp2(row_max - joint_max);
       const float other_weight = other.x == -INFINITY ? 0.0f : fast_exp2(other.x - joint_max);
-      const float joint_sum = row_sum * own_weight + other.y * other_weight;
+      float joint_sum = row_sum * own_weight + other.y * other_weight;
+      if (EXT && p.sink_values != nullptr && joint_max > -INFINITY) joint_sum += exp2f(p.sink_values[head] * kLog2e - joint_max);
       const float inverse = joint_sum > 0.0f ? 1.0f / joint_sum : 0.0f;
       const float own_factor = own_weight * inverse, other_factor = other_weight * inverse;
       const uint32_t other_o = lane_base + (group ? kColsO0 : kColsO1);
@@ -504,6 +513,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         for (int k = 0; k < 32; ++k) {
           joined[k] = own_has_tiles ? __uint_as_float(v[k]) * own_factor : 0.0f;
           if (other_has_tiles) joined[k] = fmaf(__uint_as_float(w[k]), other_factor, joined[k]);
+        }
+        if (EXT && p.gate != nullptr && row < tokens_here) {
+          const float4* gate_row = reinterpret_cast<const float4*>(
+              p.gate + static_cast<size_t>(token0 + row) * p.gate_stride + static_cast<size_t>(head) * D + col0 + c);
+#pragma unroll
+          for (int k = 0; k < 32; k += 4) {
+            const float4 z = gate_row[k >> 2];
+            joined[k] *= 1.0f / (1.0f + __expf(-z.x));
+            joined[k + 1] *= 1.0f / (1.0f + __expf(-z.y));
+            joined[k + 2] *= 1.0f / (1.0f + __expf(-z.z));
+            joined[k + 3] *= 1.0f / (1.0f + __expf(-z.w));
+          }
         }
 #pragma unroll
         for (int k = 0; k < 32; k += 8) {
@@ -848,17 +869,25 @@ bool pool_map(const void* pool, int pages, int page_size, int kv_heads, int head
   return true;
 }
 
-template <int D, bool TMA_KV>
-int launch_attention(const CUtensorMap& k_map, const CUtensorMap& v_map, const CUtensorMap& k_run_map,
-                     const CUtensorMap& v_run_map, const Params& p, dim3 grid, cudaStream_t stream) {
+template <int D, bool TMA_KV, bool EXT>
+int launch_attention_instance(const CUtensorMap& k_map, const CUtensorMap& v_map, const CUtensorMap& k_run_map,
+                              const CUtensorMap& v_run_map, const Params& p, dim3 grid, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D, TMA_KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D, TMA_KV, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  return vipera_launch(attention_prefill_tc_kernel<D, TMA_KV>, grid, dim3(kThreads), kSmemBytes, stream, k_map, v_map, k_run_map,
+  return vipera_launch(attention_prefill_tc_kernel<D, TMA_KV, EXT>, grid, dim3(kThreads), kSmemBytes, stream, k_map, v_map, k_run_map,
                        v_run_map, p);
+}
+
+template <int D, bool TMA_KV>
+int launch_attention(const CUtensorMap& k_map, const CUtensorMap& v_map, const CUtensorMap& k_run_map,
+                     const CUtensorMap& v_run_map, const Params& p, dim3 grid, cudaStream_t stream) {
+  if (p.sink_values != nullptr || p.gate != nullptr)
+    return launch_attention_instance<D, TMA_KV, true>(k_map, v_map, k_run_map, v_run_map, p, grid, stream);
+  return launch_attention_instance<D, TMA_KV, false>(k_map, v_map, k_run_map, v_run_map, p, grid, stream);
 }
 
 }  // namespace
@@ -867,12 +896,17 @@ int launch_attention(const CUtensorMap& k_map, const CUtensorMap& v_map, const C
 // meaning of the arguments; `num_pages` is the pools' first extent).  `status` is a device word
 // that must be 0 before the launch; it is non-zero afterwards when a bounded wait inside the
 // kernel ran out.
-VIPERA_API int vipera_attention_prefill_tc(const void* q, void* out, const void* k_pool, const void* v_pool,
-                                           const int* entry_starts, const int* entry_pos0, const int* block_table,
-                                           int table_width, int page_size, int num_entries, int num_tokens,
-                                           int num_heads, int num_kv_heads, int head_dim, float scale, int window,
-                                           int num_pages, int skip_single, int* status, void* stream) {
+// `sink_values` [heads] (null: none): a learned sink per query head; `gate` (null: none): 32-bit
+// pre-activations of an output gate, row t at gate + t * gate_stride, [heads * d] values (the base and
+// the stride whole multiples of four floats).
+VIPERA_API int vipera_attention_prefill_tc_gated(const void* q, void* out, const void* k_pool, const void* v_pool,
+                                                 const int* entry_starts, const int* entry_pos0, const int* block_table,
+                                                 int table_width, int page_size, int num_entries, int num_tokens,
+                                                 int num_heads, int num_kv_heads, int head_dim, float scale, int window,
+                                                 int num_pages, int skip_single, const float* sink_values,
+                                                 const float* gate, long long gate_stride, int* status, void* stream) {
   if (num_tokens <= 0 || num_entries <= 0) return VIPERA_OK;
+  if (gate && ((reinterpret_cast<uintptr_t>(gate) & 15) || (gate_stride & 3))) return VIPERA_BAD_ARGUMENT;
   if ((head_dim != 64 && head_dim != 128) || num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 || num_pages <= 0)
     return VIPERA_BAD_SHAPE;
   if (!status) return VIPERA_BAD_ARGUMENT;
@@ -893,6 +927,9 @@ VIPERA_API int vipera_attention_prefill_tc(const void* q, void* out, const void*
   p.scale = scale;
   p.skip_single = skip_single;
   p.status = status;
+  p.sink_values = sink_values;
+  p.gate = gate;
+  p.gate_stride = gate_stride;
   // at most one partly filled tile per entry beyond the full ones
   dim3 grid(num_heads, (num_tokens + kQ - 1) / kQ + num_entries);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -908,6 +945,16 @@ VIPERA_API int vipera_attention_prefill_tc(const void* q, void* out, const void*
   CUtensorMap none{};
   return head_dim == 64 ? launch_attention<64, false>(none, none, none, none, p, grid, s)
                         : launch_attention<128, false>(none, none, none, none, p, grid, s);
+}
+
+VIPERA_API int vipera_attention_prefill_tc(const void* q, void* out, const void* k_pool, const void* v_pool,
+                                           const int* entry_starts, const int* entry_pos0, const int* block_table,
+                                           int table_width, int page_size, int num_entries, int num_tokens,
+                                           int num_heads, int num_kv_heads, int head_dim, float scale, int window,
+                                           int num_pages, int skip_single, int* status, void* stream) {
+  return vipera_attention_prefill_tc_gated(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width,
+                                           page_size, num_entries, num_tokens, num_heads, num_kv_heads, head_dim, scale,
+                                           window, num_pages, skip_single, nullptr, nullptr, 0, status, stream);
 }
 
 VIPERA_API const char* vipera_attention_tc_status_text(int status) { return vipera_status_text(status); }

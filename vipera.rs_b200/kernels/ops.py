@@ -726,11 +726,26 @@ MMA_HEAD_DIMS = (64, 128)
 TC_ATTENTION_HEAD_DIMS = (64, 128)
 
 
+def _gate_pointer(gate: Optional[torch.Tensor], gate_offset: int, rows: int, width: int, what: str):
+    """(address of the first gate value, floats between rows) of a float32 [rows, >= offset + width] tensor."""
+    if gate is None:
+        return None, 0
+    if gate.dim() != 2 or gate.shape[0] != rows or gate.stride(1) != 1 or not 0 <= gate_offset <= gate.shape[1] - width:
+        raise InvalidArgumentError(f"{what}: the gate must hold heads * value size values per token")
+    return _gpu(gate, "gate", torch.float32) + 4 * int(gate_offset), int(gate.stride(0))
+
+
+def attention_tc_takes_gate(gate: Optional[torch.Tensor], gate_offset: int) -> bool:
+    """The tensor-core ending reads the gate four values at a time."""
+    return gate is None or (gate_offset % 4 == 0 and gate.stride(0) % 4 == 0 and gate.data_ptr() % 16 == 0)
+
+
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *,
                       entry_starts: torch.Tensor, entry_pos0: torch.Tensor, block_table: torch.Tensor,
                       num_entries: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                       window: int = 0, skip_single: bool = False, keep_first: int = 0, sink: bool = False,
-                      mask_chunk: int = 0) -> None:
+                      mask_chunk: int = 0, sink_values: Optional[torch.Tensor] = None,
+                      gate: Optional[torch.Tensor] = None, gate_offset: int = 0) -> None:
     """Flash-style attention of a step whose entries bring any number of tokens (bfloat16,
     head sizes 64 and 128), on tcgen05 with accumulators in tensor memory
     (VIPERA_ATTENTION_TC=0 keeps it on the mma.sync kernel).
@@ -738,7 +753,10 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
     ``keep_first`` (with a window: that many first keys stay visible) and ``sink`` (one added to the
     softmax's denominator) are served by the mma.sync kernel, and so is ``mask_chunk`` (instead of
     a window: a query sees the earlier keys of its own chunk of that many positions; the kernels
-    take it as a negative window)."""
+    take it as a negative window).  ``sink_values`` float32 [heads] (a learned sink: exp(sink_h) joins
+    head h's denominator) and ``gate`` (float32 [tokens, width]: the output is multiplied by the sigmoid
+    of the heads * d values from column ``gate_offset`` on) are served by the tcgen05 kernel's ending,
+    with a plain window only."""
     if mask_chunk:
         if window:
             raise InvalidArgumentError("attention_prefill: a mask is a window or chunks, not both")
@@ -758,6 +776,17 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
     kinds = [_c_void] * 7 + [_c_int] * 7 + [_c_float, _c_int]
     skip = 1 if skip_single else 0
     keep_first = int(keep_first or 0) if window > 0 else 0
+    if sink_values is not None or gate is not None:
+        if keep_first or window < 0 or (sink and sink_values is None) or not attention_tc_takes_gate(gate, gate_offset):
+            raise UnsupportedError("attention_prefill: a learned sink and an output gate come with a plain window only")
+        if sink_values is not None and sink_values.numel() != num_heads:
+            raise InvalidArgumentError("attention_prefill: one sink score per query head")
+        gate_pointer, gate_stride = _gate_pointer(gate, gate_offset, count, num_heads * head_dim, "attention_prefill")
+        fn = _function("attention_tc", "vipera_attention_prefill_tc_gated",
+                       kinds + [_c_int, _c_int, _c_void, _c_void, ctypes.c_longlong, _c_void, _c_void])
+        _check(fn(*pointers, *sizes, k_pool.shape[0], skip, _opt(sink_values, "sink_values", torch.float32), gate_pointer,
+                  gate_stride, kernel_status_word(q.device).data_ptr(), _stream()), "attention_prefill_tc")
+        return
     if keep_first or sink:
         fn = _function("attention_mma", "vipera_attention_prefill_kept", kinds + [_c_int, _c_int, _c_int, _c_void])
         _check(fn(*pointers, *sizes, skip, keep_first, 1 if sink else 0, _stream()), "attention_prefill")
@@ -831,7 +860,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v
                      positions: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int,
                      head_dim: int, scale: float, window: int, chunk: int, num_splits: int,
                      scratch: torch.Tensor, entry_starts: Optional[torch.Tensor] = None, keep_first: int = 0,
-                     sink: bool = False, mask_chunk: int = 0) -> None:
+                     sink: bool = False, mask_chunk: int = 0, sink_values: Optional[torch.Tensor] = None,
+                     gate: Optional[torch.Tensor] = None, gate_offset: int = 0) -> None:
     """Split-key attention of the entries that bring one token (bfloat16, head sizes 64 and
     128); the partial results of the splits are combined by a second kernel.  Without
     ``entry_starts`` every entry brings one token (q and out are [entries, heads * d], positions
@@ -840,14 +870,20 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v
     more than one token are skipped (attention_prefill with ``skip_single`` runs them).
     ``keep_first`` (with a window: that many first keys stay visible; they are one more split, so
     the scratch is sized for ``num_splits + 1``) and ``sink`` (one added to the softmax's denominator).
-    ``mask_chunk``: instead of a window, chunks of that many positions (passed on as a negative window)."""
+    ``mask_chunk``: instead of a window, chunks of that many positions (passed on as a negative window).
+    ``sink_values`` float32 [heads]: a learned sink per query head; ``gate`` float32 [rows of q, width]: the
+    output is multiplied by the sigmoid of the heads * d values from column ``gate_offset`` on."""
     if mask_chunk:
         if window:
             raise InvalidArgumentError("attention_decode: a mask is a window or chunks, not both")
         window = -int(mask_chunk)
-    fn = _function("attention_mma", "vipera_attention_decode_kept",
+    fn = _function("attention_mma", "vipera_attention_decode_gated",
                    [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
-                    _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, ctypes.c_size_t, _c_void, _c_int, _c_int, _c_void])
+                    _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, ctypes.c_size_t, _c_void, _c_int, _c_int,
+                    _c_void, _c_void, ctypes.c_longlong, _c_void])
+    if sink_values is not None and sink_values.numel() != num_heads:
+        raise InvalidArgumentError("attention_decode: one sink score per query head")
+    gate_pointer, gate_stride = _gate_pointer(gate, gate_offset, q.shape[0], num_heads * head_dim, "attention_decode")
     if head_dim not in MMA_HEAD_DIMS:
         raise UnsupportedError(f"attention_decode: head size {head_dim} (built: 64, 128)")
     count = block_table.shape[0]
@@ -864,7 +900,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v
               _gpu(block_table, "block_table", torch.int32), block_table.shape[1], k_pool.shape[1], count,
               num_heads, num_kv_heads, head_dim, float(scale), int(window or 0), int(chunk), int(num_splits),
               _gpu(scratch, "scratch", torch.float32), scratch.numel(), _opt(entry_starts, "entry_starts", torch.int32),
-              int(keep_first or 0) if window > 0 else 0, 1 if sink else 0, _stream()), "attention_decode", kernels=2)
+              int(keep_first or 0) if window > 0 else 0, 1 if sink else 0, _opt(sink_values, "sink_values", torch.float32),
+              gate_pointer, gate_stride, _stream()), "attention_decode", kernels=2)
 
 
 def attention_decode_scratch_floats(num_entries: int, num_heads: int, head_dim: int, num_splits: int) -> int:

@@ -174,10 +174,11 @@ class GQAttention(Mixer):
             own.append("attention_talk")
             if self.dtype == torch.bfloat16 and self.head_dim in ops.MMA_HEAD_DIMS and self.value_dim == self.head_dim:
                 own.append("attention_mma")
-        plain_mask = self.talk is None and self.out_scale == 1.0 and self.sink_values is None and not self.gated
+        plain_mask = self.talk is None and self.out_scale == 1.0
         if plain_mask and self.dtype == torch.bfloat16 and self.head_dim in (64, 128) and self.value_dim == self.head_dim:
             own.append("attention_mma")
-            if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS and not self.keep_first and not self.sink and not self.chunk:
+            if (self.head_dim in ops.TC_ATTENTION_HEAD_DIMS and not self.keep_first and not self.chunk
+                    and (not self.sink or self.sink_values is not None)):
                 own.append("attention_tc")
         return tuple(dict.fromkeys(tuple(own) + self.qkv.kernel_families() + self.out.kernel_families()
                                    + self.position.kernel_families()))
@@ -334,12 +335,18 @@ class GQAttention(Mixer):
                                head_dim=d, value_dim=self.value_dim, scale=self.scale, out_scale=self.out_scale,
                                split_keys=keys, num_splits=splits, stats=stats, partial=partial)
             return
+        # a learned sink and an output gate are endings of the tcgen05 flash kernel and of the split-key
+        # kernel's combine (plain windows only); elsewhere they run through the general kernel
+        extended = self.sink_values is not None or gate is not None
+        extended_ok = (not self.keep_first and not self.chunk and ops.attention_tc_takes_gate(gate, self.gate_offset)
+                       and d in ops.TC_ATTENTION_HEAD_DIMS and os.environ.get("VIPERA_ATTENTION_TC", "1") != "0")
         if (self.out_scale == 1.0 and ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d
-                and self.sink_values is None and gate is None):
+                and (not extended or extended_ok)):
             # Kept first keys and the sink are options of the mma.sync kernels (the flash kernel folds
             # the kept keys as tiles of their own, the split-key kernel as a split of its own); the
             # tcgen05 flash kernel serves attention without them.
-            kept = dict(keep_first=self.keep_first, sink=self.sink, mask_chunk=self.chunk)
+            kept = dict(keep_first=self.keep_first, sink=self.sink, mask_chunk=self.chunk, sink_values=self.sink_values,
+                        gate=gate, gate_offset=self.gate_offset)
             places = 1 if self.keep_first else 0
             if ctx.all_single:
                 chunk, splits = ops.decode_splits(ctx.num_entries, kv_heads, max(ctx.max_kv_len, 1),
