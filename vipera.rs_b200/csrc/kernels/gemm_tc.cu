@@ -874,6 +874,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
               }
               use ^= 1;
             }
+          } else if (EXT && p.epilogue == EPI_STORE && p.out_dtype == VIPERA_BF16) {
+            // A plain store into bfloat16, with the activation of a unit without a gate on the way:
+            // 64 accumulator columns make 64 outputs = one 128-byte row of bfloat16
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 64) {
+              if (row0 >= p.tokens || ty * BN + c >= p.features) continue;
+              uint8_t* buffer = mine + use * 4096;
+              if (lane == 0) tma_store_wait_read<1>();
+              __syncwarp();
+#pragma unroll 1
+              for (int q2 = 0; q2 < 2; ++q2) {
+                float v[32];
+                tmem_load_32(taddr + c + q2 * 32, v);
+                if (p.bias) {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) {
+                    const int n = ty * BN + c + q2 * 32 + i;
+                    v[i] += n < p.features ? p.bias[n] : 0.0f;
+                  }
+                }
+                if (p.activation == ACT_RELU2) {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) {
+                    const float r = fmaxf(v[i], 0.0f);
+                    v[i] = r * r;
+                  }
+                }
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                  const int chunk = (q2 * 4 + h) ^ (lane & 7);
+                  *reinterpret_cast<uint4*>(buffer + lane * 128 + chunk * 16) =
+                      make_uint4(pack_bf16x2(v[8 * h], v[8 * h + 1]), pack_bf16x2(v[8 * h + 2], v[8 * h + 3]),
+                                 pack_bf16x2(v[8 * h + 4], v[8 * h + 5]), pack_bf16x2(v[8 * h + 6], v[8 * h + 7]));
+                }
+              }
+              fence_async_shared();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&map_out, buffer, ty * BN + c, row0);
+                tma_store_commit();
+              }
+              use ^= 1;
+            }
           } else {
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
@@ -1667,6 +1710,10 @@ static int run_gemm(const void* A, const void* W, int T, int N, int K, int epilo
     } else if (epilogue == EPI_STORE && out_dtype == VIPERA_F32 && N % 4 == 0 &&
                (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
       if ((r = make_out_map(&map_out, out, T, N, false)) != VIPERA_OK) return r;
+      p.tma_ending = 1;
+    } else if (ext && epilogue == EPI_STORE && out_dtype == VIPERA_BF16 && N % 8 == 0 &&
+               (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+      if ((r = make_out_map(&map_out, out, T, N, true)) != VIPERA_OK) return r;
       p.tma_ending = 1;
     } else if (epilogue == EPI_RESIDUAL && N % 4 == 0 && (reinterpret_cast<uintptr_t>(resid) & 15) == 0) {
       if ((r = make_out_map(&map_out, resid, T, N, false)) != VIPERA_OK) return r;
