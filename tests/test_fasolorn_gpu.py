@@ -298,15 +298,18 @@ def test_long_decoding_of_several_requests():
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_replay_as_a_process(dtype):
-    path = folder_for("mixed", dtype)
-    vocab = cases.MIXED["vocab"]
+@pytest.mark.parametrize("name,page_size", [("mixed", 16), ("wide", 64)])
+def test_replay_as_a_process(name, page_size, dtype):
+    """bin/trace_run as a user starts it; the wider model with the replayer's own page size (head sizes
+    of 64 and 128: in bfloat16 the tensor-core attention with its keys by TMA)."""
+    path = folder_for(name, dtype)
+    vocab = cases.CONFIGS[name]["vocab"]
     a, b = helpers.random_tokens(vocab, 50, 1), helpers.random_tokens(vocab, 21, 2)
     builder = TraceBuilder()
     builder.step([("a", a[:30], [0, 29]), ("b", b[:2], [1])])
     builder.step([("a", a[30:31], [0]), ("b", b[2:], list(range(19)))], end=["b"])
     builder.step([("a", a[31:], list(range(19)))], end=["a"])
-    outputs = helpers.run_trace(path, dtype, builder.steps, max_tokens=128, page_size=16, max_live=4, vocab=vocab)
+    outputs = helpers.run_trace(path, dtype, builder.steps, max_tokens=128, page_size=page_size, max_live=4, vocab=vocab)
     reference = {"a": cases.plain_logits(path, a), "b": cases.plain_logits(path, b)}
     close_calls = set()
     if dtype == "bfloat16":   # where a plain router's choice hangs on a hair, bfloat16 may choose otherwise

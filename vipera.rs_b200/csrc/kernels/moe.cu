@@ -573,7 +573,7 @@ static int launch_products(const MoeParams& p, cudaStream_t s) {
 static int check_moe(const MoeParams& p) {
   if (p.experts <= 0 || p.experts > kMaxExperts || p.groups <= 0 || p.experts % p.groups || p.keep <= 0 ||
       p.keep > p.groups || p.top <= 0 || p.top > p.keep * (p.experts / p.groups) || p.group_top < 1 || p.group_top > 2 ||
-      p.hidden <= 0 || p.ff <= 0 || p.gate_group <= 0 || p.ff % p.gate_group)
+      p.hidden <= 0 || p.ff <= 0 || (p.gated && (p.gate_group <= 0 || p.ff % p.gate_group)))
     return VIPERA_BAD_SHAPE;
   if (p.identity < 0 || p.identity > p.experts || p.always < 0 || p.slots != p.top + p.always ||
       p.experts - p.identity + p.always > kMaxExperts || (p.identity > 0 && !p.rows))
