@@ -156,3 +156,53 @@ def plain_logits(path: str, tokens: Sequence[int]) -> np.ndarray:
 def plain_margins(path: str, tokens: Sequence[int]) -> np.ndarray:
     """Per position, the least margin of any router's choice (plain.route)."""
     return _plain(path, tokens)[1]
+
+
+def drawn(seed: int) -> dict:
+    """A configuration whose sizes, order of layers and constants are drawn from `seed`: head sizes with and
+    without tensor-core forms, grouped and single heads, windows shorter than a page and longer than a
+    request, layers without masks, rotations of part of a head, ranks that are no multiples of 8, mixtures
+    with and without identity outputs and shared units."""
+    import random
+
+    rng = random.Random(seed)
+    width = rng.choice([64, 96, 128, 200, 256])
+    value_row = rng.choice([32, 64, 128])        # kv_heads * vdim of every blending layer
+    layers = []
+    for _ in range(rng.randint(2, 5)):
+        kind = rng.choice(["dense", "moe", "moe", None])
+        if kind == "dense":
+            mlp = dense(rng.choice([24, 40, 64, 136]))
+        elif kind == "moe":
+            experts, identity = rng.choice([1, 2, 5, 8, 19]), rng.choice([0, 0, 1, 3])
+            ff = rng.choice([8, 16, 24, 64])
+            mlp = moe(ff=ff, experts=experts, identity=identity, top=rng.randint(1, min(experts + identity, 4)),
+                      scale=rng.choice([1.0, 0.5, 2.5]), shared=rng.choice([0, ff // 2, ff, 2 * ff + 8]))
+        else:
+            mlp = None
+        window = rng.choice([0, 1, 5, 33, 64, 65, 100, 500])
+        if rng.random() < 0.6:
+            blends = rng.random() < 0.6
+            if blends:
+                kv_heads = rng.choice([1, 2, 4])
+                vdim = value_row // kv_heads
+                dim = rng.choice([vdim, vdim, 16, 24])
+            else:
+                kv_heads = rng.choice([1, 2, 3])
+                dim = rng.choice([8, 16, 48, 64, 128])
+                vdim = rng.choice([dim, dim, 8, 40])
+            heads = kv_heads * rng.choice([1, 1, 2, 3])
+            rot_dims = rng.choice([0, 2, dim // 2 // 2 * 2, dim])
+            layers.append(attention(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, window=window, rot_dims=rot_dims,
+                                    base=rng.choice([100.0, 10000.0, 500000.0]), scale=dim ** -0.5, v_mix=blends, mlp=mlp))
+        else:
+            dim, rot_dim = rng.choice([8, 16, 32, 64]), rng.choice([2, 8, 16, 32, 64])
+            layers.append(latent(heads=rng.choice([1, 2, 3, 8]), dim=dim, rot_dim=rot_dim, vdim=rng.choice([8, 24, 64, 80]),
+                                 rank=rng.choice([16, 19, 64, 96, 136, 200]), window=window,
+                                 base=rng.choice([100.0, 10000.0]), scale=(dim + rot_dim) ** -0.5, mlp=mlp))
+    return config(layers, width=width, vocab=rng.randint(50, 600), eps=rng.choice([1e-5, 1e-6, 3e-4]),
+                  scale=rng.choice([None, 0.5, 1.0, 3.0]))
+
+
+for _seed in range(16):
+    CONFIGS[f"drawn{_seed}"] = drawn(_seed)

@@ -363,3 +363,33 @@ def test_generate_from_the_command_line():
     for index, token in enumerate(produced):
         row = logits[len(prompt) - 1 + index]
         assert float(row.max() - row[token]) <= 1e-4 * float(np.abs(row).max()), (index, token)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(16))
+def test_configurations_drawn_at_random(seed, dtype):
+    """Sizes, order of layers and constants drawn from a seed (fasolorn_cases.drawn), with pages of 64
+    keys: two requests whole, then the same two in portions of changing size beside each other and
+    token by token."""
+    name = f"drawn{seed}"
+    path = cases.folder(name, dtype, scaling="mild")
+    vocab = cases.CONFIGS[name]["vocab"]
+    a, b = helpers.random_tokens(vocab, 170, 200 + seed), helpers.random_tokens(vocab, 75, 300 + seed)
+    rp = replayer(path, dtype, 512, page_size=64)
+    judge_a, judge_b = Judge(dtype, path, a, most_skipped=0.6), Judge(dtype, path, b, most_skipped=0.6)
+    judge_a.add(whole(rp, "whole a", a), 0, "whole")
+    judge_b.add(whole(rp, "whole b", b), 0, "whole")
+    done_a = done_b = 0
+    for size_a, size_b in ((2, 40), (61, 2), (3, 1), (64, 1), (1, 30), (30, 1), (1, 0), (1, 0), (7, 0)):
+        entries = [{"id": "a", "tokens": a[done_a:done_a + size_a], "want": list(range(size_a))}]
+        if size_b:
+            entries.append({"id": "b", "tokens": b[done_b:done_b + size_b], "want": list(range(size_b))})
+        got = rp.step(entries, (["b"] if size_b and done_b + size_b == len(b) else []) + (["a"] if done_a + size_a == len(a) else []))
+        judge_a.add(got[:size_a], done_a, ("a", done_a))
+        if size_b:
+            judge_b.add(got[size_a:], done_b, ("b", done_b))
+        done_a, done_b = done_a + size_a, done_b + size_b
+    assert done_a == len(a) and done_b == len(b)
+    judge_a.close()
+    judge_b.close()
+    assert rp.pools.audit() == ""
