@@ -102,7 +102,8 @@ class FasolornConfig:
 
     @staticmethod
     def _attention(where: str, mixer: Dict[str, Any]) -> Dict[str, Any]:
-        _need(where, mixer, ("heads", "kv_heads", "dim", "vdim", "scale"))
+        _need(where, mixer, ("heads", "dim", "vdim", "scale"))
+        mixer = {"kv_heads": mixer["heads"], **mixer}      # without kv_heads every query head has keys of its own
         out = {key: _integer(f"{where}.{key}", mixer[key]) for key in ("heads", "kv_heads", "dim", "vdim")}
         if out["heads"] % out["kv_heads"]:
             raise InvalidArgumentError(f"{where}: heads {out['heads']} is not a multiple of kv_heads {out['kv_heads']}")

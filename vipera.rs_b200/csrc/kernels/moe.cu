@@ -107,27 +107,47 @@ moe_route_kernel(MoeParams p) {
   const T* h = static_cast<const T*>(p.h) + static_cast<size_t>(t) * p.hidden;
   for (int i = threadIdx.x; i < p.hidden; i += kRouteThreads) h_s[i] = to_float<T>(h[i]);
   __syncthreads();
-  for (int e = warp; e < p.experts; e += kRouteThreads / 32) {
-    const float* r = p.router + static_cast<size_t>(e) * p.hidden;
-    float sum = 0.0f;
-    if ((p.hidden & 3) == 0 && (reinterpret_cast<uintptr_t>(p.router) & 15) == 0) {
-      // four values at a time: a lane sums the products of values 4 (lane + 32 j) .. + 3, in that order
-      const float4* r4 = reinterpret_cast<const float4*>(r);
-      const float4* h4 = reinterpret_cast<const float4*>(h_s);
+  constexpr int kWarpsHere = kRouteThreads / 32;
+  if ((p.hidden & 3) == 0 && (reinterpret_cast<uintptr_t>(p.router) & 15) == 0) {
+    // Four values at a time: a lane sums the products of values 4 (lane + 32 j) .. + 3, in that order.  A warp
+    // walks four of its rows side by side, so that their loads are in flight together (a step of one token is
+    // one block, which waits for every row it asks for).
+    const float4* h4 = reinterpret_cast<const float4*>(h_s);
+    for (int e0 = warp; e0 < p.experts; e0 += 4 * kWarpsHere) {
+      const float4* rows[4];
+      float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        rows[j] = reinterpret_cast<const float4*>(p.router + static_cast<size_t>(min(e0 + j * kWarpsHere, p.experts - 1)) * p.hidden);
 #pragma unroll 4
       for (int i = lane; i < p.hidden / 4; i += 32) {
-        const float4 a = h4[i], b = r4[i];
-        sum = fmaf(a.x, b.x, sum);
-        sum = fmaf(a.y, b.y, sum);
-        sum = fmaf(a.z, b.z, sum);
-        sum = fmaf(a.w, b.w, sum);
+        const float4 a = h4[i];
+        float4 b[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[j] = rows[j][i];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          sums[j] = fmaf(a.x, b[j].x, sums[j]);
+          sums[j] = fmaf(a.y, b[j].y, sums[j]);
+          sums[j] = fmaf(a.z, b[j].z, sums[j]);
+          sums[j] = fmaf(a.w, b[j].w, sums[j]);
+        }
       }
-    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float sum = warp_sum(sums[j]);
+        if (lane == 0 && e0 + j * kWarpsHere < p.experts) score[e0 + j * kWarpsHere] = sum;
+      }
+    }
+  } else {
+    for (int e = warp; e < p.experts; e += kWarpsHere) {
+      const float* r = p.router + static_cast<size_t>(e) * p.hidden;
+      float sum = 0.0f;
 #pragma unroll 4
       for (int i = lane; i < p.hidden; i += 32) sum = fmaf(h_s[i], r[i], sum);
+      sum = warp_sum(sum);
+      if (lane == 0) score[e] = sum;
     }
-    sum = warp_sum(sum);
-    if (lane == 0) score[e] = sum;
   }
   __syncthreads();
   if (warp == 0) {
