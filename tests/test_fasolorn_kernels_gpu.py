@@ -4,6 +4,7 @@ kernel's ending, the split-key kernel's combine), rotation with published and bl
 mixture with units without a gate, a correction, identity outputs and always-used units in its three
 forms."""
 import math
+import os
 
 import numpy as np
 import pytest
@@ -100,12 +101,20 @@ def test_attention_with_a_learned_sink_and_an_output_gate(heads, kv_heads, d, pa
     wide1 = wide_d[last].contiguous()
     position1 = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
     chunk, splits = ops.decode_splits(entries, kv_heads, 300, ops.sm_count(DEV))
-    scratch = torch.full((ops.attention_decode_scratch_floats(entries, heads, d, splits),), float("nan"), device=DEV)
-    out5 = torch.full_like(q1, float("nan"))
-    ops.attention_decode(q1, out5, kp, vp, positions=position1, block_table=tb, num_heads=heads, num_kv_heads=kv_heads,
-                         head_dim=d, scale=scale, window=window, chunk=chunk, num_splits=splits, scratch=scratch,
-                         sink=True, sink_values=sink_d, gate=wide1, gate_offset=offset)
-    assert _rel(out5.float().cpu().view(entries, heads, d), want[last]) < limit
+    # the one-kernel forms (a cluster of 8 or 16 blocks per entry and KV head, with and without the next
+    # keys on their way) and the two-kernel form
+    for cluster in ("8", "8p", "16", "16p", "0"):
+        os.environ["VIPERA_ATTENTION_CLUSTER"] = cluster
+        try:
+            scratch = torch.full((ops.attention_decode_scratch_floats(entries, heads, d, splits),), float("nan"), device=DEV)
+            out5 = torch.full_like(q1, float("nan"))
+            ops.attention_decode(q1, out5, kp, vp, positions=position1, block_table=tb, num_heads=heads,
+                                 num_kv_heads=kv_heads, head_dim=d, scale=scale, window=window, chunk=chunk,
+                                 num_splits=splits, scratch=scratch, sink=True, sink_values=sink_d, gate=wide1,
+                                 gate_offset=offset)
+        finally:
+            os.environ.pop("VIPERA_ATTENTION_CLUSTER", None)
+        assert _rel(out5.float().cpu().view(entries, heads, d), want[last]) < limit, cluster
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -484,12 +484,17 @@ __device__ __forceinline__ float cluster_load(uint32_t local, uint32_t rank) {
   return value;
 }
 
-template <int D, int kClusterBlocks, bool PREFETCH>
+// EXT: the ending knows a learned sink per query head (`sink_values`, null: none) and an output gate (`gate`,
+// null: none; the entry's row at gate + entry * gate_stride holds [heads * D] 32-bit pre-activations); the
+// instances without it are the kernel as it was before those options existed.
+template <int D, int kClusterBlocks, bool PREFETCH, bool EXT = false>
 __global__ void __launch_bounds__(128, PREFETCH ? 1 : 3)
 attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                                 const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
                                 const int* __restrict__ block_table, int table_width, int page_size, int page_shift,
-                                int num_heads, int num_kv_heads, float scale, int window, __nv_bfloat16* __restrict__ out) {
+                                int num_heads, int num_kv_heads, float scale, int window, __nv_bfloat16* __restrict__ out,
+                                const float* __restrict__ sink_values, const float* __restrict__ gate,
+                                long long gate_stride) {
   constexpr int kKeys = 32;
   constexpr int kWarpTile = 2 * kKeys * D * 2;  // bytes of one warp's key and value tiles
   constexpr int kRow = D + 4;                   // floats of a partial row: D outputs, max, sum, padding
@@ -660,7 +665,10 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, const __nv_
         value += w * cluster_load(merged_addr + (head_in_group * kRow + col) * 4, b);
       }
       const int head = kv_head * group + head_in_group;
-      out[(static_cast<size_t>(entry) * num_heads + head) * D + col] = __float2bfloat16_rn(value / total);
+      if (EXT && sink_values) total += exp2f(sink_values[head] * 1.4426950408889634f - best);   // the maxima are in units of log2
+      float result = value / total;
+      if (EXT && gate) result *= 1.0f / (1.0f + expf(-gate[static_cast<size_t>(entry) * gate_stride + static_cast<size_t>(head) * D + col]));
+      out[(static_cast<size_t>(entry) * num_heads + head) * D + col] = __float2bfloat16_rn(result);
     }
   }
   // nobody leaves while its partial may still be read
@@ -745,17 +753,22 @@ static ClusterChoice cluster_decode_choice(int num_entries, int num_heads, int n
   return {0, false};
 }
 
-template <int D, int BLOCKS, bool PREFETCH>
+template <int D, int BLOCKS, bool PREFETCH, bool EXT = false>
 int launch_decode_cluster(const void* q, void* out, const void* k_pool, const void* v_pool, const int* positions,
                           const int* block_table, int table_width, int page_size, int page_shift, int num_entries,
-                          int num_heads, int num_kv_heads, float scale, int window, cudaStream_t s) {
+                          int num_heads, int num_kv_heads, float scale, int window, cudaStream_t s,
+                          const float* sink_values = nullptr, const float* gate = nullptr, long long gate_stride = 0) {
+  if (!EXT && (sink_values || gate))
+    return launch_decode_cluster<D, BLOCKS, PREFETCH, true>(q, out, k_pool, v_pool, positions, block_table, table_width,
+                                                            page_size, page_shift, num_entries, num_heads, num_kv_heads,
+                                                            scale, window, s, sink_values, gate, gate_stride);
   constexpr int kSmem = 16 * D * 2 + 4 * (PREFETCH ? 2 : 1) * (2 * 32 * D * 2) + 16 * (D + 4) * 4;
   static int configured = 0;  // 1: ready, -1: this cluster size cannot be launched here
   if (configured == 0) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_cluster_kernel<D, BLOCKS, PREFETCH>,
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_cluster_kernel<D, BLOCKS, PREFETCH, EXT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e == cudaSuccess && BLOCKS > 8)
-      e = cudaFuncSetAttribute(attention_decode_cluster_kernel<D, BLOCKS, PREFETCH>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+      e = cudaFuncSetAttribute(attention_decode_cluster_kernel<D, BLOCKS, PREFETCH, EXT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) {
       cudaGetLastError();
       configured = -1;
@@ -778,11 +791,11 @@ int launch_decode_cluster(const void* q, void* out, const void* k_pool, const vo
   attributes[1].val.clusterDim.z = BLOCKS;
   config.attrs = attributes;
   config.numAttrs = 2;
-  cudaError_t error = cudaLaunchKernelEx(&config, attention_decode_cluster_kernel<D, BLOCKS, PREFETCH>,
+  cudaError_t error = cudaLaunchKernelEx(&config, attention_decode_cluster_kernel<D, BLOCKS, PREFETCH, EXT>,
                                          static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pool),
                                          static_cast<const __nv_bfloat16*>(v_pool), positions, block_table, table_width,
                                          page_size, page_shift, num_heads, num_kv_heads, scale, window,
-                                         static_cast<__nv_bfloat16*>(out));
+                                         static_cast<__nv_bfloat16*>(out), sink_values, gate, gate_stride);
   return error == cudaSuccess ? VIPERA_OK : static_cast<int>(error);
 }
 
@@ -799,20 +812,21 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
     while ((1 << page_shift) < page_size) ++page_shift;
   }
   // the one-kernel forms serve steps of single tokens only
-  const ClusterChoice cluster = (entry_starts || keep_first > 0 || sink || gate) ? ClusterChoice{0, false}
+  // (a learned sink and a gate are endings the clusters' EXT instances know; kept keys and the sink of score 0 are not)
+  const ClusterChoice cluster = (entry_starts || keep_first > 0 || (sink && !sink_values)) ? ClusterChoice{0, false}
                                              : cluster_decode_choice(num_entries, num_heads, num_kv_heads, chunk * num_splits);
   if (cluster.blocks == 8 && cluster.prefetch)
     return launch_decode_cluster<D, 8, true>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size,
-                                             page_shift, num_entries, num_heads, num_kv_heads, scale, window, s);
+                                             page_shift, num_entries, num_heads, num_kv_heads, scale, window, s, sink_values, gate, gate_stride);
   if (cluster.blocks == 8)
     return launch_decode_cluster<D, 8, false>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size,
-                                              page_shift, num_entries, num_heads, num_kv_heads, scale, window, s);
+                                              page_shift, num_entries, num_heads, num_kv_heads, scale, window, s, sink_values, gate, gate_stride);
   if (cluster.blocks == 16 && cluster.prefetch)
     return launch_decode_cluster<D, 16, true>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size,
-                                              page_shift, num_entries, num_heads, num_kv_heads, scale, window, s);
+                                              page_shift, num_entries, num_heads, num_kv_heads, scale, window, s, sink_values, gate, gate_stride);
   if (cluster.blocks == 16)
     return launch_decode_cluster<D, 16, false>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size,
-                                               page_shift, num_entries, num_heads, num_kv_heads, scale, window, s);
+                                               page_shift, num_entries, num_heads, num_kv_heads, scale, window, s, sink_values, gate, gate_stride);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
