@@ -75,7 +75,7 @@ def visible(count, mask):
 
 
 def softmax_with_sink(scores, seen, sink):
-    """scores [H, T, T]; the denominator also holds exp(sink_h) (no key, no value).  Without a sink
+    """scores [H, T, T]; the denominator also holds exp(sink_h), a term that stands for no token.  Without a sink
     (None) an ordinary softmax."""
     scores = scores.masked_fill(~seen, float("-inf"))
     top = scores.max(dim=-1, keepdim=True).values

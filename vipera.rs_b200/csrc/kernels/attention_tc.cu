@@ -75,7 +75,7 @@ struct Params {
   int skip_single;             // entries of one token are left out (the split-key kernel runs them)
   int* status;
   // Options of the ending.  sink_values [heads] (null: none): exp(sink_h) joins head h's denominator
-  // (a learned sink: no key, no value, not scaled).  gate (null: none): the output is multiplied by
+  // (a learned sink: a term of the softmax sum that stands for no token; the score scale does not apply to it).  gate (null: none): the output is multiplied by
   // sigmoid(gate[t * gate_stride + h * d + e]), a 32-bit pre-activation.
   const float* sink_values;
   const float* gate;
