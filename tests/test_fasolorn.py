@@ -221,3 +221,20 @@ def test_what_the_sharpened_weights_make_visible():
     changed[3] = (changed[3] + 1) % cases.FAR["vocab"]
     a, b = _logits("far", tokens), _logits("far", changed)
     assert np.abs(a[-20:] - b[-20:]).max() / np.abs(a).max() > 1e-3
+
+
+def test_exact_angle_tables_stay_good_far_out():
+    """The design's tables are formed in 64-bit and rounded once: at position 100,000 an entry is as good
+    as at position 1, where a 32-bit angle is off by thousands of times more."""
+    from vipera_rs_b200.parts.rotary import rotary_tables
+
+    dims, base, reach = 16, 10000.0, 100001
+    exact = rotary_tables(dims, base, reach, "cpu", None, exact=True).pair
+    plain32 = rotary_tables(dims, base, reach, "cpu", None).pair
+    angle = torch.arange(reach, dtype=F)[:, None] * plain.frequencies(dims, base)[None, :]
+    want_cos, want_sin = torch.cos(angle), torch.sin(angle)
+    assert (exact[0].double() - want_cos).abs().max() < 1e-7 and (exact[1].double() - want_sin).abs().max() < 1e-7
+    assert (plain32[0].double() - want_cos)[-1000:].abs().max() > 1e-4
+    arch, spec = spec_of("mixed")
+    assert spec.layers[0].parts["mixer"].params["position"].params["exact_angles"] is True
+    assert spec.layers[2].parts["mixer"].params["position"].params["exact_angles"] is True

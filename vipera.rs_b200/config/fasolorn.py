@@ -196,7 +196,7 @@ def fasolorn_model_spec(config: FasolornConfig) -> ModelSpec:
             rot = m["rot"]
             position = PartSpec("none", {}) if rot is None else PartSpec("rope_interleaved", {
                 "head_dim": m["dim"], "rotary_dims": rot["dims"], "theta": rot["base"], "scaling": None,
-                "max_positions": config.max_positions})
+                "exact_angles": True, "max_positions": config.max_positions})
             value_mix = None
             if m["v_mix"]:
                 value_mix = "blend" if source_seen else "source"
@@ -209,7 +209,8 @@ def fasolorn_model_spec(config: FasolornConfig) -> ModelSpec:
         else:
             rot = m["rot"]
             position = PartSpec("rope_neox", {"head_dim": m["rot_dim"], "rotary_dims": rot["dims"], "theta": rot["base"],
-                                              "scaling": None, "max_positions": config.max_positions})
+                                              "scaling": None, "exact_angles": True,
+                                              "max_positions": config.max_positions})
             mixer = PartSpec("latent_attention", {
                 "hidden_size": config.width, "num_heads": m["heads"], "head_dim": m["dim"], "rot_dim": m["rot_dim"],
                 "value_dim": m["vdim"], "kv_rank": m["kv_rank"], "softmax_scale": m["scale"], "norm_eps": config.eps,

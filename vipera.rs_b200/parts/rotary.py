@@ -70,16 +70,26 @@ def wavelength_blend(inverse: torch.Tensor, scaling: dict) -> torch.Tensor:
     return out.to(torch.float32)
 
 
-def rotary_tables(head_dim: int, theta: float, max_positions: int, device, scaling=None) -> _Tables:
+def rotary_tables(head_dim: int, theta: float, max_positions: int, device, scaling=None, exact: bool = False) -> _Tables:
     """cos and sin, each float32 [max_positions, head_dim / 2], on ``device``; ``head_dim`` is the
     count of values that turn.  ``scaling``: None, the YaRN constants (see ``yarn_blend``), or with
-    ``kind = "llama3"`` the constants of ``wavelength_blend``."""
+    ``kind = "llama3"`` the constants of ``wavelength_blend``.  ``exact`` (without scaling): frequencies,
+    angles, cosines and sines are formed in 64-bit and rounded once, so that a table entry is as good
+    at position 100,000 as at position 1 (a 32-bit angle p f_i carries p f_i 2^-24 of error)."""
     frozen = None if not scaling else tuple(sorted((str(k), str(v)) for k, v in scaling.items()))
-    key = (head_dim, float(theta), max_positions, str(device), frozen)
+    key = (head_dim, float(theta), max_positions, str(device), frozen, bool(exact))
     cached = _TABLES.get(key)
     if cached is not None:
         return cached
     half = head_dim // 2
+    if exact and not scaling:
+        frequency = torch.pow(torch.tensor(float(theta), dtype=torch.float64),
+                              -2.0 * torch.arange(half, dtype=torch.float64) / float(head_dim))
+        angle = torch.arange(max_positions, dtype=torch.float64)[:, None] * frequency[None, :]
+        tables = _Tables(torch.cos(angle).to(torch.float32).contiguous().to(device),
+                         torch.sin(angle).to(torch.float32).contiguous().to(device))
+        _TABLES[key] = tables
+        return tables
     index = torch.arange(half, dtype=torch.float32)
     exponent = 2.0 * index / torch.tensor(float(head_dim), dtype=torch.float32)
     inverse = 1.0 / torch.pow(torch.tensor(float(theta), dtype=torch.float32), exponent)
@@ -104,7 +114,8 @@ def rotary_tables(head_dim: int, theta: float, max_positions: int, device, scali
 class RopeNeox(PositionEncoding):
     """params: ``head_dim``, ``theta``, ``max_positions`` and, optionally, ``rotary_dims`` (only
     the first that many values of a head turn, value i with value i + rotary_dims/2; default: the
-    whole head) and ``scaling`` (the YaRN constants, see ``yarn_blend``).  No tensors."""
+    whole head), ``scaling`` (the YaRN constants, see ``yarn_blend``) and ``exact_angles`` (true, without
+    scaling: the tables are formed in 64-bit and rounded once).  No tensors."""
 
     style = ops.ROPE_NEOX
     kernels = ("rope_cache",)
@@ -118,6 +129,7 @@ class RopeNeox(PositionEncoding):
         if self.rot_dims % 2 or not 0 < self.rot_dims <= self.head_dim:
             raise InvalidArgumentError(f"rotary_dims {self.rot_dims} must be even and within the head size {self.head_dim}")
         self.scaling = dict(params["scaling"]) if params.get("scaling") else None
+        self.exact = bool(params.get("exact_angles", False))
         self.reach = None   # positions the tables cover; the model's own limit where nobody says
         self._tables = None
 
@@ -137,7 +149,7 @@ class RopeNeox(PositionEncoding):
         if self._tables is None:
             if self.reach is None:
                 self.reach = self.max_positions
-            self._tables = rotary_tables(self.rot_dims, self.theta, self.reach, self.device, self.scaling)
+            self._tables = rotary_tables(self.rot_dims, self.theta, self.reach, self.device, self.scaling, self.exact)
         return self._tables.pair
 
 
